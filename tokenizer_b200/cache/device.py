@@ -30,15 +30,25 @@ class DeviceCache(CachePlan):
             self.states[call] = torch.zeros(
                 (max_requests,) + tuple(needs[call].state.shape), dtype=torch.float32,
                 device=runtime.device)
+        # what a layer's arrangement keeps beside its mixer's state: arenas of their own
+        self.side_states = {}
+        for call, need in enumerate(needs):
+            side = getattr(need, "side_state", None) if need is not None else None
+            if side is not None:
+                self.side_states[call] = torch.zeros((max_requests,) + tuple(side.shape), dtype=torch.float32,
+                                                     device=runtime.device)
         self._needs = needs
 
+    def _arenas(self):
+        return list(self.states.values()) + list(self.side_states.values())
+
     def on_open(self, cache: RequestCache) -> None:
-        for arena in self.states.values():
+        for arena in self._arenas():
             arena[cache.state_slot].zero_()
 
     def on_release(self, cache: RequestCache) -> None:
         if cache.length:            # a request that is recomputed from its first token starts from zero
-            for arena in self.states.values():
+            for arena in self._arenas():
                 arena[cache.state_slot].zero_()
 
     def bindings(self, order) -> List[CacheBinding]:
@@ -54,6 +64,7 @@ class DeviceCache(CachePlan):
                 binding.k_pool = self.pools[group][layer, 0]
                 binding.v_pool = self.pools[group][layer, 1] if self.groups[group].planes > 1 else None
             binding.state = self.states.get(source)
+            binding.side_state = self.side_states.get(source)
             out.append(binding)
         return out
 

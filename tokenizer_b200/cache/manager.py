@@ -92,7 +92,10 @@ class CachePlan:
         self.allocators = [PageAllocator(num_pages, page_size) for _ in self.groups]
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self.requests: Dict[object, RequestCache] = {}
-        shareable = len(self.groups) == 1 and self.groups[0].keeps_all and not self.state_calls
+        self.side_state_calls = [c for c, n in enumerate(needs)
+                                 if n is not None and getattr(n, "side_state", None) is not None]
+        shareable = len(self.groups) == 1 and self.groups[0].keeps_all and not self.state_calls and \
+            not self.side_state_calls
         self.share_prefixes = bool(share_prefixes and shareable)
 
     # ---- requests ------------------------------------------------------------

@@ -4,9 +4,10 @@ from .registry import (config_class_for, config_from_dict, load_config, register
 from .qwen2 import Qwen2Config
 from .pufuzen import PufuzenConfig
 from .katopel import KatopelConfig
+from .vizonex import VizonexConfig
 
 __all__ = [
-    "ConfigError", "KatopelConfig", "LayerCall", "LayerSpec", "ModelSpec", "PartSpec", "PufuzenConfig", "Qwen2Config",
+    "ConfigError", "KatopelConfig", "LayerCall", "LayerSpec", "ModelSpec", "PartSpec", "PufuzenConfig", "Qwen2Config", "VizonexConfig",
     "config_class_for", "config_from_dict", "load_config", "register_architecture",
     "registered_architectures",
 ]

@@ -7,7 +7,20 @@
 //               share[t, e] = softmax over the `top` largest logits of token t (ties: the lower
 //               index), zero elsewhere; share[t, experts] = sigmoid(the shared expert's gate logit)
 //   moe_gate    act[t, c] = f(gate[t, c]) * up[t, c] * share[t, expert of lane c], f the activation
+//
+// moe_route knows a second way to score and choose (`score` = MOE_SCORE_SIGMOID): scores s =
+// sigmoid(z); the CHOICE is made on s + correction (a learned number an expert, or none), and only
+// among the experts of the `keep` best of `groups` equal groups of neighbouring experts, a group's
+// worth being the sum of its two largest choice scores (the others count as minus infinity);
+// share[t, e] = s[e] * scale for the chosen, not renormalized.  `shared` = 2: the shared expert's
+// share is one (no gate row).  moe_gate knows a clamped activation (MOE_ACT_CLAMPED_SWISH): with
+// g = min(gate, limit) and u = clamp(up, -limit, limit), g * sigmoid(alpha g) * (u + 1); the shared
+// expert's lanes have a limit of their own.
 #include "common.cuh"
+
+enum : int { MOE_SCORE_SOFTMAX_OF_CHOSEN = 0, MOE_SCORE_SIGMOID = 1 };
+enum : int { MOE_SHARED_NONE = 0, MOE_SHARED_GATED = 1, MOE_SHARED_ONE = 2 };
+#define MOE_ACT_CLAMPED_SWISH TOKB200_ACT_COUNT
 
 #define MOE_MAX_EXPERTS 1024
 
@@ -17,8 +30,12 @@
 template <typename TI>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const TI* __restrict__ h, const float* __restrict__ w, int hidden, int experts, int top,
-                 int shared, float* __restrict__ share) {
+                 int shared_mode, float* __restrict__ share, int score, const float* __restrict__ correction,
+                 int groups, int keep, float scale) {
   __shared__ float z[MOE_MAX_EXPERTS + 1];
+  __shared__ float choice[MOE_MAX_EXPERTS];
+  const int shared = shared_mode == MOE_SHARED_GATED ? 1 : 0;      // router rows behind the experts'
+  const int columns = experts + (shared_mode != MOE_SHARED_NONE ? 1 : 0);
   pdl_wait();
   pdl_launch();
   const int t = blockIdx.x;
@@ -51,10 +68,62 @@ moe_route_kernel(const TI* __restrict__ h, const float* __restrict__ w, int hidd
     if (lane == 0) z[e] = acc;
   }
   __syncthreads();
-  float* out = share + (size_t)t * (experts + shared);
-  for (int e = threadIdx.x; e < experts; e += blockDim.x) out[e] = 0.f;
+  float* out = share + (size_t)t * columns;
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    out[e] = 0.f;
+    if (score == MOE_SCORE_SIGMOID) {
+      const float s = 1.0f / (1.0f + expf(-z[e]));
+      z[e] = s;
+      choice[e] = s + (correction ? correction[e] : 0.f);
+    }
+  }
   __syncthreads();
   if (threadIdx.x != 0) return;
+  if (score == MOE_SCORE_SIGMOID) {
+    // groups of neighbours: only the experts of the `keep` groups whose two largest choice scores
+    // add up to the most can be chosen (ties: the lower group, the lower expert)
+    const int size = experts / groups;
+    unsigned open[MOE_MAX_EXPERTS / 32];
+    for (int i = 0; i < (groups + 31) / 32; ++i) open[i] = 0u;
+    if (keep < groups) {
+      for (int k = 0; k < keep; ++k) {
+        int best = -1;
+        float worth = -INFINITY;
+        for (int g = 0; g < groups; ++g) {
+          if ((open[g >> 5] >> (g & 31)) & 1u) continue;
+          float first = -INFINITY, second = -INFINITY;
+          for (int e = g * size; e < (g + 1) * size; ++e) {
+            const float c = choice[e];
+            if (c > first) { second = first; first = c; } else if (c > second) { second = c; }
+          }
+          const float sum = size > 1 ? first + second : first;
+          if (best < 0 || sum > worth) { best = g; worth = sum; }
+        }
+        if (best < 0) break;
+        open[best >> 5] |= 1u << (best & 31);
+      }
+    }
+    unsigned taken[MOE_MAX_EXPERTS / 32];
+    for (int i = 0; i < (experts + 31) / 32; ++i) taken[i] = 0u;
+    for (int k = 0; k < top; ++k) {
+      int best = -1;
+      float value = -INFINITY;
+      for (int e = 0; e < experts; ++e) {
+        const int g = e / size;
+        if (keep < groups && !((open[g >> 5] >> (g & 31)) & 1u)) continue;
+        if (!((taken[e >> 5] >> (e & 31)) & 1u) && (best < 0 || choice[e] > value)) {
+          best = e;
+          value = choice[e];
+        }
+      }
+      if (best < 0) break;
+      taken[best >> 5] |= 1u << (best & 31);
+      out[best] = z[best] * scale;
+    }
+    if (shared_mode == MOE_SHARED_ONE) out[experts] = 1.0f;
+    if (shared_mode == MOE_SHARED_GATED) out[experts] = 1.0f / (1.0f + expf(-z[experts]));
+    return;
+  }
   unsigned taken[MOE_MAX_EXPERTS / 32];
   for (int i = 0; i < (experts + 31) / 32; ++i) taken[i] = 0u;
   float highest = 0.f, sum = 0.f;
@@ -76,14 +145,26 @@ moe_route_kernel(const TI* __restrict__ h, const float* __restrict__ w, int hidd
   }
   for (int e = 0; e < experts; ++e)
     if ((taken[e >> 5] >> (e & 31)) & 1u) out[e] /= sum;
-  if (shared) out[experts] = 1.0f / (1.0f + expf(-z[experts]));
+  if (shared_mode == MOE_SHARED_GATED) out[experts] = 1.0f / (1.0f + expf(-z[experts]));
+  if (shared_mode == MOE_SHARED_ONE) out[experts] = 1.0f;
+}
+
+// act(gate) * up of one inner lane: the activations of every gated feed-forward, and the clamped one
+__device__ __forceinline__ float moe_glu(int act, float g, float u, float limit, float alpha) {
+  if (act == MOE_ACT_CLAMPED_SWISH) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+  }
+  return gate_activation(act, g) * u;
 }
 
 // gu: [T, 2 I], gates in the first I columns, ups in the last; lanes 0 .. experts * ff belong to the
 // routed experts (ff lanes each), the lanes behind to the shared expert.
 template <typename T>
 __global__ void moe_gate_kernel(const T* __restrict__ gu, const float* __restrict__ share, T* __restrict__ out,
-                                int inner, int experts, int ff, int shared, int act, size_t n) {
+                                int inner, int experts, int ff, int shared, int act, size_t n, float limit,
+                                float shared_limit, float alpha) {
   pdl_wait();
   pdl_launch();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -95,7 +176,7 @@ __global__ void moe_gate_kernel(const T* __restrict__ gu, const float* __restric
     float value = 0.f;
     if (w != 0.f) {
       const float g = to_float(gu[t * 2 * inner + c]), u = to_float(gu[t * 2 * inner + inner + c]);
-      value = gate_activation(act, g) * u * w;
+      value = moe_glu(act, g, u, e < experts ? limit : shared_limit, alpha) * w;
     }
     out[i] = from_float<T>(value);
   }
@@ -104,7 +185,7 @@ __global__ void moe_gate_kernel(const T* __restrict__ gu, const float* __restric
 // bfloat16, inner and expert widths in whole 8s: eight consecutive lanes (one expert's) a thread
 __global__ void moe_gate_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ share,
                                        __nv_bfloat16* __restrict__ out, int inner, int experts, int ff, int shared,
-                                       int act, size_t n8) {
+                                       int act, size_t n8, float limit, float shared_limit, float alpha) {
   pdl_wait();
   pdl_launch();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -124,7 +205,8 @@ __global__ void moe_gate_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, con
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
-        h[k] = __floats2bfloat162_rn(gate_activation(act, g.x) * u.x * w, gate_activation(act, g.y) * u.y * w);
+        const float lim = e < experts ? limit : shared_limit;
+        h[k] = __floats2bfloat162_rn(moe_glu(act, g.x, u.x, lim, alpha) * w, moe_glu(act, g.y, u.y, lim, alpha) * w);
       }
       packed = *reinterpret_cast<const uint4*>(h);
     }
@@ -133,24 +215,29 @@ __global__ void moe_gate_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, con
 }
 
 TOKB200_API int tokb200_moe_route(const void* h, int h_dtype, const float* w, int hidden, int experts, int top,
-                                  int shared, float* share, int n_rows, cudaStream_t stream) {
+                                  int shared, float* share, int n_rows, int score, const float* correction,
+                                  int groups, int keep, float scale, cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
   if (hidden <= 0 || experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || top > experts ||
-      (shared != 0 && shared != 1))
+      shared < MOE_SHARED_NONE || shared > MOE_SHARED_ONE ||
+      (score != MOE_SCORE_SOFTMAX_OF_CHOSEN && score != MOE_SCORE_SIGMOID) || groups <= 0 || experts % groups ||
+      keep <= 0 || keep > groups || (long long)keep * (experts / groups) < top)
     return TOKB200_BAD_SIZE;
   if (h_dtype == TOKB200_F32)
     return launch_dependent(moe_route_kernel<float>, dim3(n_rows), dim3(128), 0, stream, (const float*)h, w, hidden,
-                            experts, top, shared, share);
+                            experts, top, shared, share, score, correction, groups, keep, scale);
   if (h_dtype == TOKB200_BF16)
     return launch_dependent(moe_route_kernel<__nv_bfloat16>, dim3(n_rows), dim3(128), 0, stream,
-                            (const __nv_bfloat16*)h, w, hidden, experts, top, shared, share);
+                            (const __nv_bfloat16*)h, w, hidden, experts, top, shared, share, score, correction, groups,
+                            keep, scale);
   return TOKB200_BAD_DTYPE;
 }
 
 TOKB200_API int tokb200_moe_gate(const void* gu, const float* share, void* out, int dtype, int n_rows, int inner,
-                                 int experts, int ff, int shared, int act, cudaStream_t stream) {
+                                 int experts, int ff, int shared, int act, float limit, float shared_limit,
+                                 float alpha, cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
-  if (inner <= 0 || experts <= 0 || ff <= 0 || (long long)experts * ff > inner || act < 0 || act >= TOKB200_ACT_COUNT ||
+  if (inner <= 0 || experts <= 0 || ff <= 0 || (long long)experts * ff > inner || act < 0 || act > MOE_ACT_CLAMPED_SWISH ||
       (!shared && (long long)experts * ff != inner))
     return TOKB200_BAD_SIZE;
   const size_t n = (size_t)n_rows * inner;
@@ -158,15 +245,15 @@ TOKB200_API int tokb200_moe_gate(const void* gu, const float* share, void* out, 
   const dim3 grid((unsigned)(blocks < 8192 ? blocks : 8192));
   if (dtype == TOKB200_F32)
     return launch_dependent(moe_gate_kernel<float>, grid, dim3(256), 0, stream, (const float*)gu, share, (float*)out,
-                            inner, experts, ff, shared, act, n);
+                            inner, experts, ff, shared, act, n, limit, shared_limit, alpha);
   if (dtype == TOKB200_BF16 && inner % 8 == 0 && ff % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
     const size_t n8 = n / 8, blocks8 = (n8 + 255) / 256;
     return launch_dependent(moe_gate_bf16x8_kernel, dim3((unsigned)(blocks8 < 65535 ? blocks8 : 65535)), dim3(256), 0,
                             stream, (const __nv_bfloat16*)gu, share, (__nv_bfloat16*)out, inner, experts, ff, shared,
-                            act, n8);
+                            act, n8, limit, shared_limit, alpha);
   }
   if (dtype == TOKB200_BF16)
     return launch_dependent(moe_gate_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)gu,
-                            share, (__nv_bfloat16*)out, inner, experts, ff, shared, act, n);
+                            share, (__nv_bfloat16*)out, inner, experts, ff, shared, act, n, limit, shared_limit, alpha);
   return TOKB200_BAD_DTYPE;
 }

@@ -8,6 +8,11 @@
 //
 // proj: [T, ld]; columns at .. : q (heads * dim), k (kv_heads * dim), v (kv_heads * vdim).
 // bias: float32, indexed like proj's columns from `at` on (or null).  A block a token.
+//
+// With `q_gain` / `k_gain` (float32, one a column of q and of k): before the rotation the token's
+// whole q projection (all heads at once) is divided by its root mean square, eps inside the root,
+// and multiplied by q_gain; the same for k.  With `temp` (float32, one a query head): the head's
+// queries are multiplied by it, which multiplies the head's scores.  All of it in 32-bit.
 #include "common.cuh"
 
 template <typename TI, typename T>
@@ -16,7 +21,9 @@ __global__ void qkv_rotate_store_kernel(const TI* __restrict__ proj, int ld, int
                                         const int* __restrict__ pos, const int* __restrict__ slot,
                                         const int* __restrict__ row_req, T* __restrict__ q_out,
                                         T* __restrict__ k_pool, T* __restrict__ v_pool, int heads, int kv_heads,
-                                        int dim, int vdim, int row) {
+                                        int dim, int vdim, int row, const float* __restrict__ q_gain,
+                                        const float* __restrict__ k_gain, float eps, const float* __restrict__ temp) {
+  __shared__ float scratch[33];
   const int t = blockIdx.x;
   const int r = row_req[t];
   const int p = pos[t];
@@ -26,22 +33,41 @@ __global__ void qkv_rotate_store_kernel(const TI* __restrict__ proj, int ld, int
   if (r < 0) return;
   const TI* in = proj + (size_t)t * ld + at;
   const int lanes = (heads + 2 * kv_heads) * row;
+  float q_inv = 1.f, k_inv = 1.f;
+  if (q_gain != nullptr || k_gain != nullptr) {         // root mean squares over the whole projections
+    float qs = 0.f, ks = 0.f;
+    for (int col = threadIdx.x; col < (heads + kv_heads) * dim; col += blockDim.x) {
+      const float v = to_float(in[col]) + (bias ? bias[col] : 0.f);
+      if (col < heads * dim) qs = fmaf(v, v, qs); else ks = fmaf(v, v, ks);
+    }
+    qs = block_sum(qs, scratch);
+    ks = block_sum(ks, scratch);
+    if (q_gain != nullptr) q_inv = 1.0f / sqrtf(qs / (float)(heads * dim) + eps);
+    if (k_gain != nullptr) k_inv = 1.0f / sqrtf(ks / (float)(kv_heads * dim) + eps);
+  }
   for (int i = threadIdx.x; i < lanes; i += blockDim.x) {
     const int head = i / row, l = i % row;
     if (head < heads + kv_heads) {                       // a query or key head: bias, rotation
       float value = 0.f;
       if (l < dim) {
         const int col = head * dim + l;
+        const bool query = head < heads;
+        const float* gain = query ? q_gain : k_gain;
+        const float inv = query ? q_inv : k_inv;
+        const int first = query ? 0 : heads * dim;       // the gains are indexed inside q and inside k
         value = to_float(in[col]) + (bias ? bias[col] : 0.f);
+        if (gain != nullptr) value = value * inv * gain[col - first];
         if (l < rot_dims) {
           const int mate = col ^ 1;
-          const float other = to_float(in[mate]) + (bias ? bias[mate] : 0.f);
+          float other = to_float(in[mate]) + (bias ? bias[mate] : 0.f);
+          if (gain != nullptr) other = other * inv * gain[mate - first];
           float s, c;
           sincosf((float)p * inv_freq[l >> 1], &s, &c);
           value = (l & 1) ? value * c + other * s : value * c - other * s;
         }
       }
       if (head < heads) {
+        if (temp != nullptr) value *= temp[head];
         q_out[((size_t)t * heads + head) * row + l] = from_float<T>(value);
       } else if (where >= 0) {
         k_pool[((size_t)where * kv_heads + (head - heads)) * row + l] = from_float<T>(value);
@@ -62,7 +88,8 @@ TOKB200_API int tokb200_qkv_rotate_store(const void* proj, int proj_dtype, int l
                                          const float* inv_freq, int rot_dims, const int* pos, const int* slot,
                                          const int* row_req, void* q_out, void* k_pool, void* v_pool,
                                          int out_dtype, int n_rows, int heads, int kv_heads, int dim, int vdim,
-                                         int row, cudaStream_t stream) {
+                                         int row, const float* q_gain, const float* k_gain, float eps,
+                                         const float* temp, cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
   if (heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0 || row < dim || row < vdim || rot_dims < 0 ||
       rot_dims % 2 || rot_dims > dim || (rot_dims > 0 && inv_freq == nullptr))
@@ -70,7 +97,7 @@ TOKB200_API int tokb200_qkv_rotate_store(const void* proj, int proj_dtype, int l
 #define LAUNCH(TI, T)                                                                                         \
   return launch_dependent(qkv_rotate_store_kernel<TI, T>, dim3(n_rows), dim3(256), 0, stream, (const TI*)proj, \
                           ld, at, bias, inv_freq, rot_dims, pos, slot, row_req, (T*)q_out, (T*)k_pool,        \
-                          (T*)v_pool, heads, kv_heads, dim, vdim, row)
+                          (T*)v_pool, heads, kv_heads, dim, vdim, row, q_gain, k_gain, eps, temp)
   if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_F32) LAUNCH(float, float);
   if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_BF16) LAUNCH(float, __nv_bfloat16);
   if (proj_dtype == TOKB200_BF16 && out_dtype == TOKB200_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);

@@ -1244,42 +1244,175 @@ def gdn_out_norm(o: torch.Tensor, gate: torch.Tensor, g_at: int, gain: torch.Ten
 
 # ---- queries, keys and values with unlike head sizes; routed experts ----
 def qkv_rotate_store(proj: torch.Tensor, at: int, bias, inv_freq, rot_dims: int, pos, slot, row_req, q_out, k_pool,
-                     v_pool, heads: int, kv_heads: int, dim: int, vdim: int, row: int) -> None:
+                     v_pool, heads: int, kv_heads: int, dim: int, vdim: int, row: int, q_gain=None, k_gain=None,
+                     eps: float = 0.0, temp=None) -> None:
     """Bias, interleaved rotation of the first `rot_dims` lanes of every query and key head, and the
     cache write, from `proj`'s columns at .. (q, k, v); rows of `row` lanes a head, zero behind dim
-    (queries, keys) and vdim (values).  `slot` None: no cache write."""
+    (queries, keys) and vdim (values).  `slot` None: no cache write.  `q_gain` / `k_gain` (float32, one a
+    column of q / of k): the whole q (k) projection of a token is divided by its root mean square (`eps`
+    inside the root) and multiplied by the gain first; `temp` (float32, one a query head) multiplies
+    the head's queries."""
     n = proj.shape[0]
     if tuple(q_out.shape) != (n, heads * row) or k_pool.dtype != q_out.dtype or v_pool.dtype != q_out.dtype or \
             at + heads * dim + kv_heads * (dim + vdim) > proj.shape[1]:
         raise ValueError("qkv_rotate_store: q_out is [T, heads * row] in the cache's type, the columns inside proj")
+    for gain, size in ((q_gain, heads * dim), (k_gain, kv_heads * dim), (temp, heads)):
+        if gain is not None and (gain.dtype != torch.float32 or gain.numel() != size):
+            raise ValueError("qkv_rotate_store: gains are float32, one a column of q and of k; temperatures one a head")
     _check(_lib("rotary_store").tokb200_qkv_rotate_store(
         _sliced_ptr(proj), _i(_tag(proj)), _i(_ld(proj)), _i(at), _ptr(bias), _ptr(inv_freq), _i(rot_dims), _ptr(pos),
         _ptr(slot), _ptr(row_req), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _i(_tag(q_out)), _i(n), _i(heads),
-        _i(kv_heads), _i(dim), _i(vdim), _i(row), _stream()), "qkv_rotate_store")
+        _i(kv_heads), _i(dim), _i(vdim), _i(row), _ptr(q_gain), _ptr(k_gain), _f(eps), _ptr(temp), _stream()),
+        "qkv_rotate_store")
 
 
-def moe_route(h: torch.Tensor, w: torch.Tensor, experts: int, top: int, shared: bool, share: torch.Tensor) -> None:
+MOE_SCORES = {"softmax_of_chosen": 0, "sigmoid": 1}
+MOE_SHARED = {None: 0, "gated": 1, "one": 2}
+MOE_ACTIVATIONS = dict(ACTIVATIONS, clamped_swish=len(ACTIVATIONS))
+
+
+def moe_route(h: torch.Tensor, w: torch.Tensor, experts: int, top: int, shared, share: torch.Tensor,
+              score: str = "softmax_of_chosen", correction: Optional[torch.Tensor] = None, groups: int = 1,
+              keep: int = 1, scale: float = 1.0) -> None:
     """Router logits z = w h in 32-bit (`w` float32 [experts (+ 1), hidden]; `h` float32 or bfloat16), then
-    share[t, e] = softmax over token t's `top` largest logits, zero for the other experts; with
-    `shared`, share[t, experts] = sigmoid(z[t, experts])."""
+    every expert's share of the token, zero where it is not chosen.  `score` "softmax_of_chosen": the `top`
+    largest logits, share = softmax over them.  "sigmoid": s = sigmoid(z); the choice is made on s +
+    `correction` (float32, one an expert, or None) among the experts of the `keep` best of `groups` equal
+    groups of neighbours (a group's worth: the sum of its two largest choice scores); share = s * `scale`.
+    `shared`: None / False (no shared expert), "gated" / True (share[t, experts] = sigmoid of one more router
+    row), "one" (share[t, experts] = 1)."""
     n, hidden = h.shape
-    rows = experts + int(shared)
+    shared = {True: "gated", False: None}.get(shared, shared)
+    rows = experts + int(shared == "gated")
+    columns = experts + int(shared is not None)
     if w.dtype != torch.float32 or tuple(w.shape) != (rows, hidden) or share.dtype != torch.float32 or \
-            tuple(share.shape) != (n, rows):
+            tuple(share.shape) != (n, columns):
         raise ValueError("moe_route: float32 router rows [experts (+ 1), hidden], shares float32 [T, experts (+ 1)]")
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != experts):
+        raise ValueError("moe_route: the correction is float32, one an expert")
     _check(_lib("moe").tokb200_moe_route(_ptr(h), _i(_tag(h)), _ptr(w), _i(hidden), _i(experts), _i(top),
-                                         _i(int(shared)), _ptr(share), _i(n), _stream()), "moe_route")
+                                         _i(MOE_SHARED[shared]), _ptr(share), _i(n), _i(MOE_SCORES[score]),
+                                         _ptr(correction), _i(groups), _i(keep), _f(scale), _stream()), "moe_route")
 
 
 def moe_gate(gu: torch.Tensor, share: torch.Tensor, out: torch.Tensor, experts: int, ff: int, shared: bool,
-             activation: str = "silu") -> None:
+             activation: str = "silu", limit: float = 0.0, shared_limit: float = 0.0, alpha: float = 1.0) -> None:
     """out[t, c] = act(gu[t, c]) * gu[t, I + c] * share[t, expert of lane c]: lanes 0 .. experts * ff
-    are the routed experts' (ff each), the lanes behind the shared expert's."""
+    are the routed experts' (ff each), the lanes behind the shared expert's.  `activation` is one of
+    MOE_ACTIVATIONS; "clamped_swish": with g = min(gate, limit), u = clamp(up, -limit, limit), the lane is
+    g * sigmoid(alpha g) * (u + 1) (`shared_limit` for the shared expert's lanes)."""
     n, inner = out.shape
     if gu.shape[1] != 2 * inner or gu.dtype != out.dtype or tuple(share.shape) != (n, experts + int(shared)):
         raise ValueError("moe_gate: input [T, 2 I], output [T, I] of one type, shares [T, experts (+ 1)]")
+    if activation not in MOE_ACTIVATIONS:
+        raise ValueError(f"moe_gate: activation is one of {', '.join(MOE_ACTIVATIONS)}")
     _check(_lib("moe").tokb200_moe_gate(_ptr(gu), _ptr(share), _ptr(out), _i(_tag(gu)), _i(n), _i(inner), _i(experts),
-                                        _i(ff), _i(int(shared)), _i(activation_tag(activation)), _stream()), "moe_gate")
+                                        _i(ff), _i(int(shared)), _i(MOE_ACTIVATIONS[activation]), _f(limit),
+                                        _f(shared_limit), _f(alpha), _stream()), "moe_gate")
+
+
+# ---- a short convolution across steps; a layer whose sublayers share one norm; learned positions ----
+CONV_ACTIVATIONS = {None: 0, "silu": 1}
+
+
+def short_conv(x: torch.Tensor, at: int, channels: int, w: torch.Tensor, bias, state, off: int, row_req, q_start,
+               state_slot, out: torch.Tensor, activation=None, residual: bool = False) -> None:
+    """out[t, c] = f(sum_j w[c, j] x[t - (taps - 1) + j, at + c] + bias[c]) (+ x[t, at + c] with `residual`)
+    over the rows of each request; rows before a request's first row of the step are the taps - 1 inputs kept
+    in `state` (float32 [slots, n], at `off` in the request's slot, [taps - 1, channels]).  `w` float32
+    [channels, taps]; `out` [T, channels] dense."""
+    n = x.shape[0]
+    taps = w.shape[1]
+    if w.dtype != torch.float32 or tuple(w.shape) != (channels, taps) or tuple(out.shape) != (n, channels) or \
+            at + channels > x.shape[1] or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != channels)) or \
+            (taps > 1 and (state is None or state.dtype != torch.float32 or state.dim() != 2)):
+        raise ValueError("short_conv: taps float32 [channels, taps], out [T, channels], a float32 state [slots, n]")
+    _check(_lib("short_conv").tokb200_short_conv(
+        _sliced_ptr(x), _i(_tag(x)), _i(_ld(x)), _i(at), _i(channels), _i(taps), _ptr(w), _ptr(bias),
+        _ptr(state if taps > 1 else None), _ll(state.shape[1] if taps > 1 else 0), _i(off), _ptr(row_req), _ptr(q_start),
+        _ptr(state_slot), _i(CONV_ACTIVATIONS[activation]), _i(int(residual)), _ptr(out), _i(_tag(out)), _i(n),
+        _stream()), "short_conv")
+
+
+def short_conv_state(x: torch.Tensor, at: int, channels: int, taps: int, state: torch.Tensor, off: int, q_start,
+                     state_slot) -> None:
+    """The kept inputs of `short_conv` move on by the step's rows; launch it behind the convolution."""
+    if taps <= 1:
+        return
+    if state.dtype != torch.float32 or state.dim() != 2 or at + channels > x.shape[1]:
+        raise ValueError("short_conv_state: a float32 state [slots, n], the channels inside x")
+    _check(_lib("short_conv").tokb200_short_conv_state(
+        _sliced_ptr(x), _i(_tag(x)), _i(_ld(x)), _i(at), _i(channels), _i(taps), _ptr(state), _ll(state.shape[1]),
+        _i(off), _ptr(q_start), _ptr(state_slot), _i(q_start.shape[0] - 1), _stream()), "short_conv_state")
+
+
+def scaled_add_norm(x: torch.Tensor, terms, gain: Optional[torch.Tensor] = None, eps: float = 0.0,
+                    out: Optional[torch.Tensor] = None) -> None:
+    """x += sum of vector * term over one or two `terms` ((tensor [T, H] or float32 partial sums [S, T, H],
+    float32 vector [H])), in place (x float32); with `gain`, also out = x / sqrt(mean(x^2) + eps) * gain of
+    the new x."""
+    n_rows, hidden = x.shape
+    if x.dtype != torch.float32 or not 1 <= len(terms) <= 2 or \
+            any(v.dtype != torch.float32 or v.numel() != hidden for _, v in terms):
+        raise ValueError("scaled_add_norm: x float32 [T, H], one or two terms with float32 vectors of H")
+    if gain is not None and (out is None or tuple(out.shape) != (n_rows, hidden) or gain.numel() != hidden):
+        raise ValueError("scaled_add_norm: the norm behind the add needs a gain of H and out [T, H]")
+    args = []
+    for term in list(terms) + [None] * (2 - len(terms)):
+        if term is None:
+            args += [_ptr(None), _i(F32), _i(1), _ll(0), _ptr(None)]
+        else:
+            y, v = term
+            n_partials, stride = _partials(y, x)
+            args += [_ptr(y), _i(_tag(y)), _i(n_partials), _ll(stride), _ptr(v)]
+    _check(_lib("short_conv").tokb200_scaled_add_norm(
+        _ptr(x), *args, _ptr(gain), _f(eps), _ptr(out), _i(_tag(out) if out is not None else F32), _i(n_rows),
+        _i(hidden), _stream()), "scaled_add_norm")
+
+
+def embed_positions(ids: torch.Tensor, pos: torch.Tensor, row_req: torch.Tensor, table: torch.Tensor,
+                    positions: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] * scale + positions[pos[t]], float32."""
+    n, hidden = out.shape
+    if table.dtype != positions.dtype or table.shape[1] != hidden or positions.shape[1] != hidden:
+        raise ValueError("embed_positions: both tables have rows of the stream's width and one type")
+    _check(_lib("short_conv").tokb200_embed_positions(
+        _ptr(ids), _ptr(pos), _ptr(row_req), _ptr(table), _ptr(positions), _i(_tag(table)), _ptr(out), _i(n), _i(hidden),
+        _i(table.shape[0]), _i(positions.shape[0]), _f(scale), _stream()), "embed_positions")
+
+
+# ---- the selective state-space recurrence (scalar decay a head) ----
+MAMBA2_MAX_STATE = 256
+
+
+def mamba2_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_at: int, dt_bias, a_log, skip, heads: int, groups: int,
+                vdim: int, n_state: int, state: torch.Tensor, q_start, state_slot, y: torch.Tensor) -> None:
+    """Per head and token: dt = softplus(proj[dt_at + head] + dt_bias); S <- exp(-exp(a_log) dt) S + dt B x^T;
+    y = S^T C + skip x, over every request's rows.  `xbc` float32 [T, heads * vdim + 2 groups * n_state] (x, B,
+    C); `state` float32 [slots, n] with a slot's matrices [heads, vdim, n_state] at its start; `y` float32
+    [T, heads * vdim]."""
+    n = xbc.shape[0]
+    if xbc.dtype != torch.float32 or y.dtype != torch.float32 or tuple(y.shape) != (n, heads * vdim) or \
+            xbc.shape[1] != heads * vdim + 2 * groups * n_state or state.dtype != torch.float32 or state.dim() != 2 or \
+            dt_at + heads > proj.shape[1] or any(v.dtype != torch.float32 or v.numel() != heads for v in (dt_bias, a_log, skip)):
+        raise ValueError("mamba2_scan: sizes of the inputs, the state or the output disagree")
+    _check(_lib("mamba2").tokb200_mamba2_scan(
+        _ptr(xbc), _i(xbc.shape[1]), _sliced_ptr(proj), _i(_tag(proj)), _i(_ld(proj)), _i(dt_at), _ptr(dt_bias), _ptr(a_log),
+        _ptr(skip), _i(heads), _i(groups), _i(vdim), _i(n_state), _ptr(state), _ll(state.shape[1]), _ptr(q_start),
+        _ptr(state_slot), _i(q_start.shape[0] - 1), _ptr(y), _stream()), "mamba2_scan")
+
+
+def mamba2_out_norm(y: torch.Tensor, proj: torch.Tensor, z_at: int, gain: torch.Tensor, eps: float, parts: int,
+                    row_req, out: torch.Tensor) -> None:
+    """out = (y * silu(proj[:, z_at ..])) divided by its root mean square inside each of `parts` equal parts of
+    the row (eps inside the root), times `gain` (float32, one a lane)."""
+    n, inner = y.shape
+    if y.dtype != torch.float32 or tuple(out.shape) != (n, inner) or gain.dtype != torch.float32 or gain.numel() != inner or \
+            z_at + inner > proj.shape[1] or inner % parts:
+        raise ValueError("mamba2_out_norm: y float32 [T, inner], a gain of inner, the gate's columns inside proj")
+    _check(_lib("mamba2").tokb200_mamba2_out_norm(
+        _ptr(y), _sliced_ptr(proj), _i(_tag(proj)), _i(_ld(proj)), _i(z_at), _ptr(gain), _f(eps), _i(inner), _i(parts),
+        _ptr(row_req), _ptr(out), _i(_tag(out)), _i(n), _stream()), "mamba2_out_norm")
 
 
 # ---- read-only streams in the decoding kernels' access patterns (bench.py --stream-probe) ----

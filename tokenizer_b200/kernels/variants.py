@@ -24,6 +24,8 @@ def all_variants():
         ("delta_rule.cu", (), ()),
         ("rotary_store.cu", (), ()),
         ("moe.cu", (), ()),
+        ("short_conv.cu", (), ()),
+        ("mamba2.cu", (), ()),
     ]
     for head_dim in (16, 32, 48, 64, 128):
         jobs.append(("attention_decode.cu", (f"HEAD_DIM={head_dim}",), ()))

@@ -383,6 +383,13 @@ class RotaryGQAttention(PagedAttention):
         if p.get("bias", True):
             out += [TensorSpec(x + ".q.b", (heads * dim,)), TensorSpec(x + ".k.b", (groups * dim,)),
                     TensorSpec(x + ".v.b", (groups * vdim,))]
+        if p.get("qk_norm"):
+            out += [TensorSpec(x + ".q.norm", (heads * dim,), "one_plus_normal", 0.1),
+                    TensorSpec(x + ".k.norm", (groups * dim,), "one_plus_normal", 0.1)]
+        if p.get("head_temperature"):
+            out.append(TensorSpec(x + ".temp", (heads,), "one_plus_normal", 0.2))
+        if p.get("sink"):
+            out.append(TensorSpec(x + ".sink", (heads,), "normal", 1.0))
         return out
 
     def __init__(self, spec, store, runtime):
@@ -409,6 +416,14 @@ class RotaryGQAttention(PagedAttention):
         self.bias = None
         if p.get("bias", True):
             self.bias = runtime.vector(torch.cat([store.get(x + f".{n}.b").to(torch.float32) for n in "qkv"]))
+        self.q_gain = self.k_gain = self.temp = None
+        self.norm_eps = float(p.get("norm_eps", 0.0))
+        if p.get("qk_norm"):
+            self.q_gain, self.k_gain = runtime.vector(store.get(x + ".q.norm")), runtime.vector(store.get(x + ".k.norm"))
+        if p.get("head_temperature"):
+            self.temp = runtime.vector(store.get(x + ".temp"))
+        if p.get("sink"):
+            self.sink = runtime.vector(store.get(x + ".sink"))
         w_o = store.get(x + ".o")
         if self.row != self.vdim:           # zero columns where the value lanes end
             wide = torch.zeros((self.hidden, self.nh, self.row), dtype=w_o.dtype)
@@ -435,7 +450,8 @@ class RotaryGQAttention(PagedAttention):
         q = self.runtime.empty(ctx.n_tokens, self.nh * self.row)
         ops.qkv_rotate_store(proj, at, self.bias, self.position.inv_freq if self.position is not None else None,
                              self.rot_dims, ctx.pos, group.slots if cache.writes else None, ctx.row_req, q,
-                             cache.k_pool, cache.v_pool, self.nh, self.nkv, self.dim, self.vdim, self.row)
+                             cache.k_pool, cache.v_pool, self.nh, self.nkv, self.dim, self.vdim, self.row,
+                             q_gain=self.q_gain, k_gain=self.k_gain, eps=self.norm_eps, temp=self.temp)
         mixed = self.runtime.empty(ctx.n_tokens, self.nh * self.row)
         self.attend(q, mixed, ctx, group, cache)
         return self.out.forward(mixed, partials_ok=True)

@@ -31,6 +31,11 @@ Interfaces (duck-typed; the classes below marked "interface" document them):
   injection     tensors(spec); __init__(spec, store, runtime); needs_embedding (bool);
                 forward(stream, embedded) (changes the stream in front of a call of the order;
                 `embedded` is the embedding's output, kept for the parts that ask for it)
+  filter        tensors(spec); __init__(spec, store, runtime); state_need() -> StateNeed | None;
+                forward(h [T,H], ctx, state) -> what a sublayer reads instead of h (it may keep
+                its last inputs per request in `state`, the arena of the call's side state)
+  scale         tensors(spec); __init__(spec, store, runtime); vector (float32 [H]): a learned
+                scale, element by element, on a sublayer's output before it is added
 """
 from __future__ import annotations
 
@@ -42,7 +47,8 @@ import torch
 from ..config.spec import ConfigError, PartSpec
 from ..kernels import ops
 
-CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head", "gate", "injection")
+CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head", "gate", "injection",
+              "filter", "scale")
 _REGISTRY: Dict[str, Dict[str, Any]] = {c: {} for c in CATEGORIES}
 
 
@@ -117,8 +123,14 @@ class StateNeed:
 
 @dataclass(frozen=True)
 class CacheNeed:
+    """What one call of the order keeps per request: keys and values in pages (`kv`), the mixer's
+    state (`state`) and, beside it, a state of whatever the layer's arrangement puts around the
+    mixer (`side_state`: the last inputs of a convolution in front of it, say).  The two states are
+    arenas of their own, so a mixer with a state needs to know nothing of the arrangement."""
+
     kv: Optional[KVNeed] = None
     state: Optional[StateNeed] = None
+    side_state: Optional[StateNeed] = None
 
 
 @dataclass
@@ -208,6 +220,7 @@ class CacheBinding:
     k_pool: Optional[torch.Tensor] = None     # [pages * page_size, kv_heads, head_dim]
     v_pool: Optional[torch.Tensor] = None     # None where the group keeps one row a token
     state: Optional[torch.Tensor] = None      # [state slots, *shape] float32
+    side_state: Optional[torch.Tensor] = None # [state slots, *shape] float32: the arrangement's, not the mixer's
     writes: bool = True
 
 
@@ -233,6 +246,15 @@ class ScaledTerms:
     terms: List[Tuple[torch.Tensor, float]]
 
 
+@dataclass
+class VectorScaledTerms:
+    """Sublayer outputs that are each multiplied, element by element, by a learned vector over the
+    width before they are added: [(y, vector float32 [H])], y [T, H] or float32 partial sums
+    [S, T, H] (a layer whose mixer and feed-forward read one norm adds both at once)."""
+
+    terms: List[Tuple[torch.Tensor, torch.Tensor]]
+
+
 class ResidualStream:
     """The residual sum, kept in float32.  A part's output is not added at once:
     it stays pending until the next norm, which adds it while it reads the row
@@ -247,12 +269,16 @@ class ResidualStream:
         self._pending: Optional[torch.Tensor] = None
         self._gated: Optional[GatedDelta] = None
         self._normed = None      # (terms, norm): a sublayer's output that is normed before it is added
+        self._scaled: Optional[VectorScaledTerms] = None     # outputs still to be scaled by their vectors
 
     @property
     def pending(self) -> Optional[torch.Tensor]:
         if self._normed is not None:
             (terms, post), self._normed = self._normed, None
             post.add_to(self.x, terms)            # in place: nothing stays pending
+        if self._scaled is not None:
+            scaled, self._scaled = self._scaled, None
+            ops.scaled_add_norm(self.x, scaled.terms)      # in place as well
         if self._gated is not None:
             g, self._gated = self._gated, None
             self._pending = torch.empty(self.x.shape, dtype=torch.float32, device=self.x.device)
@@ -261,7 +287,7 @@ class ResidualStream:
 
     @pending.setter
     def pending(self, value: Optional[torch.Tensor]) -> None:
-        self._pending, self._gated, self._normed = value, None, None
+        self._pending, self._gated, self._normed, self._scaled = value, None, None, None
 
     def add(self, delta) -> None:
         self.flush()
@@ -277,6 +303,12 @@ class ResidualStream:
         offers `add_to(x, terms, then=None)`."""
         self.flush()
         self._normed = (delta.terms if isinstance(delta, ScaledTerms) else [(delta, 1.0)], post)
+
+    def add_scaled(self, delta: VectorScaledTerms) -> None:
+        """x += sum of vector * output: stays pending, so that a norm that offers `forward_scaled`
+        scales, adds and norms in one kernel."""
+        self.flush()
+        self._scaled = delta
 
     def add_gated(self, delta: GatedDelta) -> None:
         self.flush()
@@ -299,6 +331,10 @@ class ResidualStream:
         if self._normed is not None:
             (terms, post), self._normed = self._normed, None
             return post.add_to(self.x, terms, then=norm)
+        scaled = getattr(norm, "forward_scaled", None)
+        if self._scaled is not None and scaled is not None:
+            terms, self._scaled = self._scaled, None
+            return scaled(self.x, terms)
         fused = getattr(norm, "forward_gated", None)
         if self._gated is not None and fused is not None and self.x.shape[0] <= self.GATED_NORM_ROWS:
             gated, self._gated = self._gated, None

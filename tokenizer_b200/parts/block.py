@@ -192,3 +192,91 @@ class PassEntry:
 register_part("block", "sandwich_norm_residual", SandwichNormResidual)
 register_part("block", "sandwich_norm_mixer_only", SandwichNormMixerOnly)
 register_part("injection", "pass_entry", PassEntry)
+
+
+class LayerScale:
+    """A learned vector over the width that multiplies a sublayer's output, element by element, before it
+    is added to the stream.  One tensor [hidden], named outright (`tensor`)."""
+
+    @staticmethod
+    def tensors(spec):
+        return [TensorSpec(spec.params["tensor"], (spec.params["hidden_size"],), "one_plus_normal")]
+
+    def __init__(self, spec, store, runtime):
+        self.vector = runtime.vector(store.get(spec.params["tensor"]))
+
+
+class CausalConvResidual:
+    """What a sublayer reads instead of the normed stream h: h + conv(h), a causal convolution over time
+    on each channel, conv(h)_t = sum_j w[:, j] h_(t - taps + 1 + j) with zeros before a sequence's start
+    (tensor `tensor` [hidden, taps], no bias).  The last taps - 1 inputs of every request are kept between
+    steps (`state_need`), so a prompt cut anywhere gives what the whole prompt gives."""
+
+    @staticmethod
+    def tensors(spec):
+        return [TensorSpec(spec.params["tensor"], (spec.params["hidden_size"], spec.params["taps"]), "normal", 0.3)]
+
+    def __init__(self, spec, store, runtime):
+        self.runtime = runtime
+        self.hidden, self.taps = int(spec.params["hidden_size"]), int(spec.params["taps"])
+        if not 1 <= self.taps <= 16:
+            raise ValueError(f"a short convolution has 1 to 16 taps, found {self.taps}")
+        self.weight = runtime.vector(store.get(spec.params["tensor"]))
+
+    def state_need(self):
+        from .base import StateNeed
+        return StateNeed(((self.taps - 1) * self.hidden,)) if self.taps > 1 else None
+
+    def forward(self, h, ctx, state):
+        out = self.runtime.empty(h.shape[0], self.hidden)
+        ops.short_conv(h, 0, self.hidden, self.weight, None, state, 0, ctx.row_req, ctx.q_start, ctx.state_slot, out,
+                       residual=True)
+        ops.short_conv_state(h, 0, self.hidden, self.taps, state, 0, ctx.q_start, ctx.state_slot)
+        return out
+
+
+class ParallelResidual:
+    """Both sublayers on ONE norm: with h = norm(x), x += s1 * mixer(filter(h)) + s2 * feed_forward(h), s1
+    and s2 learned vectors over the width (`LayerScale`), `filter` what stands between the norm and the
+    mixer (`CausalConvResidual`; the feed-forward reads h as it is).  The two outputs stay pending on the
+    stream with their vectors, so that the next norm scales, adds and norms in one kernel.  The filter's
+    kept inputs are this arrangement's own state beside the mixer's (`CacheNeed.side_state`)."""
+
+    PARTS = {"mixer": "mixer", "mixer_norm": "norm", "mixer_filter": "filter", "mixer_scale": "scale",
+             "feed_forward": "feed_forward", "feed_forward_scale": "scale"}
+
+    def __init__(self, mixer, mixer_norm, mixer_filter, mixer_scale, feed_forward=None, feed_forward_scale=None):
+        self.mixer, self.mixer_norm, self.mixer_filter, self.mixer_scale = mixer, mixer_norm, mixer_filter, mixer_scale
+        self.feed_forward, self.feed_forward_scale = feed_forward, feed_forward_scale
+
+    def cache_need(self):
+        from .base import CacheNeed
+        need = self.mixer.cache_need()
+        return CacheNeed(kv=need.kv, state=need.state, side_state=self.mixer_filter.state_need())
+
+    def streamed_weights(self):
+        out = []
+        for part in (self.mixer, self.feed_forward):
+            out += list(getattr(part, "streamed_weights", lambda: [])())
+        return out
+
+    def forward(self, stream, ctx, cache):
+        from .base import VectorScaledTerms
+        h = stream.normed(self.mixer_norm)
+        terms = [(self.mixer.forward(self.mixer_filter.forward(h, ctx, cache.side_state), ctx, cache),
+                  self.mixer_scale.vector)]
+        if self.feed_forward is not None:
+            terms.append((self.feed_forward.forward(h), self.feed_forward_scale.vector))
+        stream.add_scaled(VectorScaledTerms(terms))
+
+
+class ParallelResidualMixerOnly(ParallelResidual):
+    """The same arrangement for a layer without a feed-forward."""
+
+    PARTS = {"mixer": "mixer", "mixer_norm": "norm", "mixer_filter": "filter", "mixer_scale": "scale"}
+
+
+register_part("scale", "layer_scale", LayerScale)
+register_part("filter", "causal_conv_residual", CausalConvResidual)
+register_part("block", "parallel_residual", ParallelResidual)
+register_part("block", "parallel_residual_mixer_only", ParallelResidualMixerOnly)

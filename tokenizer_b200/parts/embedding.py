@@ -15,20 +15,33 @@ from .norm import tensor_name
 class TokenEmbedding:
     @staticmethod
     def tensors(spec):
-        return [TensorSpec(tensor_name(spec),
-                           (spec.params["vocab_size"], spec.params["hidden_size"]))]
+        out = [TensorSpec(tensor_name(spec), (spec.params["vocab_size"], spec.params["hidden_size"]))]
+        if spec.params.get("position_tensor"):
+            out.append(TensorSpec(spec.params["position_tensor"], (spec.params["positions"], spec.params["hidden_size"])))
+        return out
 
     def __init__(self, spec, store, runtime):
         self.runtime = runtime
         self.vocab, self.hidden = int(spec.params["vocab_size"]), int(spec.params["hidden_size"])
         self.table = runtime.matrix(store.get(tensor_name(spec)))
+        # `position_tensor` (optional): a learned vector per position, [positions, hidden], added to the
+        # looked-up row as it is (the model then says `wants_positions` and is handed the rows' positions)
+        self.positions = None
+        if spec.params.get("position_tensor"):
+            self.positions = runtime.matrix(store.get(spec.params["position_tensor"]))
+        self.wants_positions = self.positions is not None
         # `scale` (optional): the looked-up row is multiplied by it, in float32; a head tied to
         # the table uses the table itself, without it
         self.scale = float(spec.params.get("scale", 1.0))
 
-    def forward(self, ids):
+    def forward(self, ids, pos=None, row_req=None):
         x = self.runtime.empty(ids.shape[0], self.hidden, dtype=torch.float32)
-        ops.embed(ids, self.table, x, self.scale)
+        if self.positions is not None:
+            if pos is None or row_req is None:
+                raise ValueError("this embedding adds a vector per position: it needs the rows' positions")
+            ops.embed_positions(ids, pos, row_req, self.table, self.positions, x, self.scale)
+        else:
+            ops.embed(ids, self.table, x, self.scale)
         return x
 
 

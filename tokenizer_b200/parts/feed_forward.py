@@ -169,7 +169,15 @@ class RoutedMLP:
     choose (`csrc/moe.cu`); the down product over all lanes is the weighted sum of the chosen
     experts' outputs.  Nothing depends on values read back to the host, so a step can be captured.
     It costs experts / top times the routed experts' arithmetic: what a model of few experts pays
-    for products of full size instead of a product per expert over gathered rows."""
+    for products of full size instead of a product per expert over gathered rows.
+
+    Parameters beyond the sizes: `score` ("softmax_of_chosen" as above; "sigmoid": scores
+    s = sigmoid(z), the choice made on s + `<prefix>.correction` (with `correction`) among the experts
+    of the `group_keep` best of `groups` equal groups of neighbours, a group's worth the sum of its two
+    largest choice scores, weights s * `route_scale`, not renormalized); `shared_gate` (False: the shared
+    expert counts fully and `.shared.sg` does not exist); `activation` (one of `ops.MOE_ACTIVATIONS`;
+    "clamped_swish" with `limit`, `shared_limit` and `alpha`: g = min(gate, limit), u = clamp(up, -limit,
+    limit), g sigmoid(alpha g) (u + 1))."""
 
     @staticmethod
     def tensors(spec):
@@ -183,7 +191,11 @@ class RoutedMLP:
         if p.get("shared_inner"):
             s = p["shared_inner"]
             out += [TensorSpec(x + ".shared.gate", (s, hidden)), TensorSpec(x + ".shared.up", (s, hidden)),
-                    TensorSpec(x + ".shared.down", (hidden, s)), TensorSpec(x + ".shared.sg", (1, hidden))]
+                    TensorSpec(x + ".shared.down", (hidden, s))]
+            if p.get("shared_gate", True):
+                out.append(TensorSpec(x + ".shared.sg", (1, hidden)))
+        if p.get("correction"):
+            out.append(TensorSpec(x + ".correction", (p["experts"],), "normal", 0.1))
         return out
 
     def __init__(self, spec, store, runtime):
@@ -192,18 +204,31 @@ class RoutedMLP:
         self.experts, self.top, self.ff = int(p["experts"]), int(p["top"]), int(p["expert_inner"])
         self.shared = int(p.get("shared_inner") or 0)
         self.activation = p.get("activation", "silu")
-        if self.activation not in ops.ACTIVATIONS:
-            raise ConfigError(f"routed feed-forward knows the activations {', '.join(ops.ACTIVATIONS)}; "
+        if self.activation not in ops.MOE_ACTIVATIONS:
+            raise ConfigError(f"routed feed-forward knows the activations {', '.join(ops.MOE_ACTIVATIONS)}; "
                               f"found {self.activation}")
         if not 1 <= self.top <= self.experts or self.experts > 1024:
             raise ConfigError(f"a token uses 1 .. experts of at most 1024 experts; found top {self.top} of {self.experts}")
+        self.score = p.get("score", "softmax_of_chosen")
+        self.groups, self.group_keep = int(p.get("groups", 1)), int(p.get("group_keep", 1))
+        self.route_scale = float(p.get("route_scale", 1.0))
+        self.limit, self.shared_limit = float(p.get("limit", 0.0)), float(p.get("shared_limit", 0.0))
+        self.alpha = float(p.get("alpha", 1.0))
+        if self.score not in ops.MOE_SCORES:
+            raise ConfigError(f"a router scores by one of {', '.join(ops.MOE_SCORES)}; found {self.score}")
+        if self.groups < 1 or self.experts % self.groups or not 1 <= self.group_keep <= self.groups or \
+                self.group_keep * (self.experts // self.groups) < self.top:
+            raise ConfigError(f"{self.experts} experts in {self.groups} equal groups of which {self.group_keep} are kept "
+                              f"cannot give a token {self.top} experts")
+        self.shared_mode = None if not self.shared else "gated" if p.get("shared_gate", True) else "one"
+        self.correction = runtime.vector(store.get(x + ".correction")) if p.get("correction") else None
         names = [f"{x}.e{e}" for e in range(self.experts)] + ([x + ".shared"] if self.shared else [])
         self.inner = self.experts * self.ff + self.shared
         gates = torch.cat([store.get(n + ".gate") for n in names], dim=0)
         ups = torch.cat([store.get(n + ".up") for n in names], dim=0)
         self.gate_up = Linear(runtime.matrix(torch.cat([gates, ups], dim=0)))
         self.down = Linear(runtime.matrix(torch.cat([store.get(n + ".down") for n in names], dim=1)))
-        rows = [store.get(x + ".router")] + ([store.get(x + ".shared.sg")] if self.shared else [])
+        rows = [store.get(x + ".router")] + ([store.get(x + ".shared.sg")] if self.shared_mode == "gated" else [])
         self.router = runtime.vector(torch.cat(rows, dim=0))       # float32: the logits are 32-bit
 
     def streamed_weights(self):
@@ -212,9 +237,11 @@ class RoutedMLP:
     def forward(self, h):
         n = h.shape[0]
         share = torch.empty((n, self.experts + (1 if self.shared else 0)), dtype=torch.float32, device=h.device)
-        ops.moe_route(h, self.router, self.experts, self.top, bool(self.shared), share)
+        ops.moe_route(h, self.router, self.experts, self.top, self.shared_mode, share, score=self.score,
+                      correction=self.correction, groups=self.groups, keep=self.group_keep, scale=self.route_scale)
         act = self.runtime.empty(n, self.inner)
-        ops.moe_gate(self.gate_up.forward(h), share, act, self.experts, self.ff, bool(self.shared), self.activation)
+        ops.moe_gate(self.gate_up.forward(h), share, act, self.experts, self.ff, bool(self.shared), self.activation,
+                     limit=self.limit, shared_limit=self.shared_limit, alpha=self.alpha)
         return self.down.forward(act, partials_ok=True)
 
 

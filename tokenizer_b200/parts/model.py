@@ -147,8 +147,10 @@ class DecoderModel:
         there, or None where the call reads an earlier call's cache."""
         needs = []
         for call in self.order:
-            needs.append(None if call.cache is not None
-                         else self.blocks[call.layer].mixer.cache_need())
+            block = self.blocks[call.layer]
+            # an arrangement that keeps something per request beside its mixer says so itself
+            need = getattr(block, "cache_need", block.mixer.cache_need)
+            needs.append(None if call.cache is not None else need())
         return needs
 
     def forward(self, ctx: StepContext, bindings: List[CacheBinding],
@@ -159,7 +161,10 @@ class DecoderModel:
             return self._forward(ctx, bindings, want_rows)
 
     def _forward(self, ctx, bindings, want_rows):
-        stream = ResidualStream(self.embedding.forward(ctx.ids))
+        if getattr(self.embedding, "wants_positions", False):
+            stream = ResidualStream(self.embedding.forward(ctx.ids, ctx.pos, ctx.row_req))
+        else:
+            stream = ResidualStream(self.embedding.forward(ctx.ids))
         # norms add in place: a part that adds the embedding's output again later gets a copy
         embedded = stream.x.clone() if self._keep_embedding else None
         ahead = self._prefetcher(ctx)

@@ -41,6 +41,12 @@ class RMSNorm:
         ops.gated_add_rms_norm(x, gated.y, gated.bias, gated.pre, gated.pre_bias, self.gain, self.eps, out)
         return out
 
+    def forward_scaled(self, x, scaled):
+        """x += sum of vector * output over `scaled.terms`, then the norm of the new x: one kernel."""
+        out = self.runtime.empty(x.shape[0], self.size)
+        ops.scaled_add_norm(x, scaled.terms, self.gain, self.eps, out)
+        return out
+
     def forward(self, x, delta=None, rows=None):
         n = x.shape[0] if rows is None else rows.shape[0]
         out = self.runtime.empty(n, self.size)

@@ -215,5 +215,87 @@ class GatedDeltaNet:
         return self.forward_projected(self.inputs.forward(h, out_dtype=torch.float32), 0, ctx, cache)
 
 
+class Mamba2:
+    """The selective state-space mixer with a scalar decay a head (Mamba-2).  With inner = heads * vdim,
+    N = `state` lanes and G = `groups`: the input product W_in h is [z: inner | x: inner | B: G N | C: G N |
+    dt: heads].  x, B and C together pass a short causal convolution over time, channel by channel
+    (`.conv` [channels, taps], bias `.conv.b`, the last tap on the current token, zeros before a sequence's
+    start), and silu.  dt = softplus(dt + `.dt_bias`).  Per head (head h reads the B and C of group
+    h // (heads / G)) a matrix S (N x vdim) from zero:
+        S <- exp(-exp(A_log) dt) S + dt B x^T;   y = S^T C + D x.
+    y, heads side by side, times silu(z), is divided by its root mean square inside each of `norm_groups`
+    equal parts of the row (`eps` inside the root), multiplied by `.norm` and goes through `.o`.
+
+    The input product is written in float32; the convolution, dt, the decay, the recurrence, its state, the
+    gate and the norm are 32-bit whatever the products' precision (`csrc/short_conv.cu`, `csrc/mamba2.cu`).
+    Per request it keeps, in one state slot, the heads' matrices ([heads, vdim, N]) and behind them the
+    convolution's last taps - 1 inputs."""
+
+    graph_safe = True    # launches depend on device-side metadata alone
+
+    @staticmethod
+    def tensors(spec):
+        p, x = spec.params, spec.prefix
+        hidden, heads, vdim, n, groups, taps = p["hidden_size"], p["heads"], p["vdim"], p["state"], p["groups"], p["conv"]
+        inner, channels = heads * vdim, heads * vdim + 2 * groups * n
+        return [TensorSpec(x + ".in", (2 * inner + 2 * groups * n + heads, hidden)),
+                TensorSpec(x + ".conv", (channels, taps), "normal", 0.5), TensorSpec(x + ".conv.b", (channels,), "normal", 0.1),
+                TensorSpec(x + ".dt_bias", (heads,), "normal", 0.5), TensorSpec(x + ".A_log", (heads,), "normal", 0.5),
+                TensorSpec(x + ".D", (heads,), "one_plus_normal", 0.2), TensorSpec(x + ".norm", (inner,), "one_plus_normal"),
+                TensorSpec(x + ".o", (hidden, inner))]
+
+    def __init__(self, spec, store, runtime):
+        p, x = spec.params, spec.prefix
+        self.runtime = runtime
+        self.hidden = int(p["hidden_size"])
+        self.heads, self.vdim, self.n, self.groups = int(p["heads"]), int(p["vdim"]), int(p["state"]), int(p["groups"])
+        self.taps, self.norm_groups, self.eps = int(p["conv"]), int(p["norm_groups"]), float(p["eps"])
+        self.inner = self.heads * self.vdim
+        self.channels = self.inner + 2 * self.groups * self.n
+        if self.groups <= 0 or self.heads % self.groups:
+            raise ConfigError(f"{self.heads} heads do not divide into {self.groups} groups")
+        if self.norm_groups <= 0 or self.inner % self.norm_groups:
+            raise ConfigError(f"{self.inner} lanes do not divide into {self.norm_groups} parts for the norm")
+        if not 1 <= self.n <= ops.MAMBA2_MAX_STATE or not 1 <= self.taps <= 16:
+            raise ConfigError(f"the state-space recurrence takes states of up to {ops.MAMBA2_MAX_STATE} lanes and "
+                              f"convolutions of up to 16 taps; found {self.n} and {self.taps}")
+        self.inputs = Linear(runtime.matrix(stacked_rows([store.get(x + ".in")])))
+        self.conv_w = runtime.vector(store.get(x + ".conv"))
+        self.conv_b = runtime.vector(store.get(x + ".conv.b"))
+        self.dt_bias = runtime.vector(store.get(x + ".dt_bias"))
+        self.a_log = runtime.vector(store.get(x + ".A_log"))
+        self.skip = runtime.vector(store.get(x + ".D"))
+        self.gain = runtime.vector(store.get(x + ".norm"))
+        self.out = Linear(runtime.matrix(store.get(x + ".o")))
+        # a slot: [heads, vdim, N] and behind it [taps - 1, channels], in whole 4s of floats
+        self.conv_off = self.heads * self.vdim * self.n
+        self.state_floats = -(-(self.conv_off + (self.taps - 1) * self.channels) // 4) * 4
+
+    def cache_need(self):
+        return CacheNeed(state=StateNeed((self.state_floats,)))
+
+    def shape_key(self, q_lens):
+        return "ssm1" if max(q_lens) == 1 else "ssm"
+
+    def streamed_weights(self):
+        return [self.inputs.weight, self.out.weight]
+
+    def forward(self, h, ctx, cache):
+        n = ctx.n_tokens
+        proj = self.inputs.forward(h, out_dtype=torch.float32)
+        xbc = torch.empty((n, self.channels), dtype=torch.float32, device=proj.device)
+        ops.short_conv(proj, self.inner, self.channels, self.conv_w, self.conv_b, cache.state, self.conv_off, ctx.row_req,
+                       ctx.q_start, ctx.state_slot, xbc, activation="silu")
+        ops.short_conv_state(proj, self.inner, self.channels, self.taps, cache.state, self.conv_off, ctx.q_start,
+                             ctx.state_slot)
+        y = torch.empty((n, self.inner), dtype=torch.float32, device=proj.device)
+        ops.mamba2_scan(xbc, proj, self.inner + self.channels, self.dt_bias, self.a_log, self.skip, self.heads,
+                        self.groups, self.vdim, self.n, cache.state, ctx.q_start, ctx.state_slot, y)
+        gated = self.runtime.empty(n, self.inner)
+        ops.mamba2_out_norm(y, proj, 0, self.gain, self.eps, self.norm_groups, ctx.row_req, gated)
+        return self.out.forward(gated, partials_ok=True)
+
+
+register_part("mixer", "mamba2", Mamba2)
 register_part("mixer", "min_gru", MinGRU)
 register_part("mixer", "gated_delta_net", GatedDeltaNet)
