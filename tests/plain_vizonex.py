@@ -131,7 +131,8 @@ def route(h, w, p, r):
     times `scale`."""
     s = sigmoid(linear(h, w[p + "router"]))
     choice = s + w[p + "correction"]
-    E, count, keep = r["experts"], r["groups"]["count"], r["groups"]["keep"]
+    groups = r.get("groups") or {"count": 1, "keep": 1}
+    E, count, keep = r["experts"], groups["count"], groups["keep"]
     grouped = choice.view(-1, count, E // count)
     group_score = grouped.topk(min(2, E // count), dim=-1).values.sum(dim=-1)
     kept = group_score.topk(keep, dim=-1).indices
