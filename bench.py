@@ -3,7 +3,7 @@
 weights on one B200.  Prints ONE JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
-                    [--config 0.5b|1.5b-mixed|7b|pufuzen|katopel]
+                    [--config 0.5b|1.5b-mixed|7b|pufuzen|katopel|vizonex]
 
 A "step" is one decode step of the whole batch.  `value` is decoded tokens a
 second timed on the device over K steps that never return to the host
@@ -196,11 +196,12 @@ def main():
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=SIZES["num_hidden_layers"])
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--config", default="0.5b", choices=["0.5b", "1.5b-mixed", "7b", "pufuzen", "katopel"],
+    parser.add_argument("--config", default="0.5b", choices=["0.5b", "1.5b-mixed", "7b", "pufuzen", "katopel", "vizonex"],
                         help="0.5b: the headline line; 7b: the same at Qwen2.5-7B sizes with 8,192-token "
                              "contexts; 1.5b-mixed: 32 requests through the scheduler at Qwen2.5-1.5B sizes; "
                              "pufuzen: prefill and decoding of the Pufuzen design at two widths beside Qwen2 at "
-                             "equal width, depth and parameters, and its kernels alone; katopel: the same for the Katopel design")
+                             "equal width, depth and parameters, and its kernels alone; katopel: the same for the Katopel design; "
+                             "vizonex: the Vizonex design beside the Katopel design at equal width, depth and parameters")
     parser.add_argument("--context", type=int, default=8192, help="--config 7b: tokens held before decoding")
     parser.add_argument("--layer-phases", action="store_true",
                         help="print where the time of the whole-layer kernel (TOKB200_LAYER=fused) goes, phase by "
@@ -215,7 +216,7 @@ def main():
     parser.add_argument("--only-decode", action="store_true",
                         help="time the decode steps only and print a short line (for profiling)")
     parser.add_argument("--only-kernels", action="store_true",
-                        help="--config katopel: the kernels alone, without the models")
+                        help="--config katopel, vizonex: the kernels alone, without the models")
     parser.add_argument("--only-prefill", action="store_true",
                         help="time the 2,048-token prefill only and print a short line (for profiling)")
     args = parser.parse_args()
@@ -241,6 +242,8 @@ def main():
         return run_pufuzen(args)
     if args.config == "katopel":
         return run_katopel(args)
+    if args.config == "vizonex":
+        return run_vizonex(args)
     args.steps = max(1, min(args.steps, NEW_TOKENS - args.warmup - 1))
 
     import torch
@@ -1073,6 +1076,230 @@ def run_katopel(args):
         "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup, "dtype": "bf16",
         "data": "synthetic: random weights drawn on the device, uniform random token ids",
         "config": {"sizes": KATOPEL_SIZES, "prefill_tokens": PREFILL_TOKENS, "decode_context": context,
+                   "peaks": pk["source"], "hbm_gbs": pk["hbm_gbs"],
+                   "l2": "kernels alone: inputs larger than L2 and a 256 MB write between timed launches"},
+        "models": models, "kernels": kernels}))
+    return 0
+
+
+# ---- the Vizonex design beside the Katopel design at equal width, depth and parameter count ----
+VIZONEX_SIZES = {
+    # width; the attention (heads over kv heads of dim / vdim lanes, chunks of `chunk` positions); the state-space
+    # mixer (heads of vdim lanes, `state` lanes in `groups` groups, taps, parts of the output norm); experts (of
+    # which a token uses `top`, inside the best `keep` of `egroups` groups) and a shared one; taps in front of every
+    # mixer.  The dense feed-forward's width is chosen so that the model has the parameters of the Katopel model
+    # of the same name.
+    "1k": dict(width=1024, heads=16, kv_heads=4, dim=64, vdim=64, chunk=1024, s_heads=16, s_vdim=64, state=128, groups=1,
+               conv=4, norm_groups=1, experts=8, top=2, egroups=2, keep=1, expert_ff=704, shared_ff=1408, taps=4,
+               vocab=32000, layers=8, positions=4096),
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, chunk=1024, s_heads=64, s_vdim=64, state=128, groups=8,
+               conv=4, norm_groups=8, experts=8, top=2, egroups=4, keep=2, expert_ff=1408, shared_ff=2816, taps=4,
+               vocab=32000, layers=8, positions=4096),
+}
+
+
+def vizonex_config(z, ff):
+    """Layers in the pattern state space + dense, attention + experts, state space + experts, attention + dense."""
+    import tokenizer_b200 as tb
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5, "groups": {"count": z["egroups"], "keep": z["keep"]}},
+           "shared": {"ff": z["shared_ff"], "limit": 7.0}}
+    ssm = {"heads": z["s_heads"], "vdim": z["s_vdim"], "state": z["state"], "groups": z["groups"], "conv": z["conv"],
+           "norm_groups": z["norm_groups"]}
+    attn = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+            "mask": {"size": z["chunk"]}}
+    pattern = [{"type": "mamba2", "mixer": ssm, "mlp": dense}, {"type": "attention", "mixer": attn, "mlp": moe},
+               {"type": "mamba2", "mixer": ssm, "mlp": moe}, {"type": "attention", "mixer": attn, "mlp": dense}]
+    return tb.config.VizonexConfig.from_dict({
+        "architecture": "Vizonex", "vocab": z["vocab"], "width": z["width"], "max_positions": z["positions"],
+        "norm": {"eps": 1e-6}, "canon": {"taps": z["taps"]}, "layers": [pattern[i % 4] for i in range(z["layers"])]})
+
+
+def run_vizonex(args):
+    """Prefill (one step of 2,048 tokens) and decoding (batch 1 and `--batch`, 2,048-token contexts) of the
+    Vizonex design at two widths, beside the closest design that was there, Katopel (a recurrence with a matrix
+    state a head, attention inside chunks, routed experts), at the same width and depth with the dense
+    feed-forward width that gives both the same parameters; then the design's own kernels alone beside the like
+    kernels of the other paths, each on inputs larger than L2, against the measured copy peak."""
+    import torch
+    import tokenizer_b200 as tb
+    from tokenizer_b200.kernels import ops
+    from tokenizer_b200.parts.model import declared_tensors
+
+    torch.cuda.set_device(0)
+    pk = peaks()
+    gen = torch.Generator().manual_seed(99)
+    context, steps = 2048, max(8, min(args.steps, 64))
+    timed = device_timed
+    count = lambda config: sum(int(torch.tensor(t.shape).prod()) for t in declared_tensors(config.model_spec()))
+
+    models = {}
+    for name, z in VIZONEX_SIZES.items():
+        if args.only_kernels:
+            break
+        beside = katopel_config(KATOPEL_SIZES[name])
+        base, step = count(vizonex_config(z, 128)), count(vizonex_config(z, 256)) - count(vizonex_config(z, 128))
+        ff = max(1, round((count(beside) - base) / step) + 1) * 128
+        models[name] = {"vizonex": dict(measure_design(vizonex_config(z, ff), z["vocab"], args, gen, context, steps), ff=ff),
+                        "katopel": measure_design(beside, z["vocab"], args, gen, context, steps)}
+
+    # ---- kernels alone: inputs larger than L2, a 256 MB write between the timed launches ----
+    dev = "cuda:0"
+    flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)
+
+    def kernel_time(fn, reps=7):
+        times = []
+        for _ in range(3 + reps):
+            flush.zero_()
+            ms, _ = timed(fn)
+            times.append(ms)
+        return sorted(times[3:])[reps // 2]
+
+    kernels = {}
+
+    def record(name, ms, nbytes, like, flops=None):
+        kernels[name] = {"us": round(ms * 1e3, 1), "gb_s": round(nbytes / (ms / 1e3) / 1e9), "like": like,
+                         "of_measured_copy_peak": round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 2)}
+        if flops is not None:
+            kernels[name]["fp32_tflops"] = round(flops / (ms / 1e3) / 1e12, 1)
+
+    ints = lambda values: torch.tensor(list(values), dtype=torch.int32, device=dev)
+    rnd = lambda *shape, dtype=torch.float32: torch.randn(*shape, device=dev, dtype=torch.float32).to(dtype)
+    T, H, I = 8192, 2048, 5632
+    # the state-space mixer at the 2k size: 64 heads of 64 lanes, 128 state lanes in 8 groups, 4 taps
+    heads, groups, vdim, n_state, taps, parts = 64, 8, 64, 128, 4, 8
+    inner, channels = heads * vdim, heads * vdim + 2 * groups * n_state
+    conv_off = heads * vdim * n_state
+    slot_floats = -(-(conv_off + (taps - 1) * channels) // 4) * 4
+    proj = rnd(T, inner + channels + heads)
+    conv_w, conv_b = rnd(channels, taps), rnd(channels)
+    a_log, dt_bias, skip = rnd(heads), rnd(heads), rnd(heads)
+    xbc = torch.empty(T, channels, device=dev)
+    y = torch.empty(T, inner, device=dev)
+    y16 = torch.empty(T, inner, dtype=torch.bfloat16, device=dev)
+    gain_i = torch.ones(inner, device=dev)
+    for requests in (1, 4):
+        state = torch.zeros(requests, slot_floats, device=dev)
+        spans, slots = ints(T * r // requests for r in range(requests + 1)), ints(range(requests))
+        row_req = ints(r for r in range(requests) for _ in range(T // requests))
+        record(f"short_conv with silu, {T} tokens of {requests} request(s), {channels} channels of {taps} taps",
+               kernel_time(lambda: ops.short_conv(proj, inner, channels, conv_w, conv_b, state, conv_off, row_req, spans, slots,
+                                                  xbc, activation="silu")), T * channels * 8, "gdn_prepare")
+        record(f"mamba2_scan, {T} tokens of {requests} request(s), {heads} heads of {n_state} x {vdim}",
+               kernel_time(lambda: ops.mamba2_scan(xbc, proj, inner + channels, dt_bias, a_log, skip, heads, groups, vdim,
+                                                   n_state, state, spans, slots, y)),
+               T * (channels + heads + inner) * 4, "gdn_scan", flops=T * heads * n_state * vdim * 4)
+    record(f"mamba2_out_norm, {T} tokens x {inner} lanes in {parts} parts",
+           kernel_time(lambda: ops.mamba2_out_norm(y, proj, 0, gain_i, 1e-6, parts, row_req, y16)), T * inner * (4 + 4 + 2),
+           "gdn_out_norm")
+    rows = 64
+    state = torch.zeros(rows, slot_floats, device=dev)
+    spans, slots = ints(range(rows + 1)), ints(range(rows))
+    record(f"mamba2_scan, {rows} requests of one token, {heads} heads of {n_state} x {vdim}",
+           kernel_time(lambda: ops.mamba2_scan(xbc[:rows], proj[:rows], inner + channels, dt_bias, a_log, skip, heads, groups,
+                                               vdim, n_state, state, spans, slots, y[:rows])),
+           rows * conv_off * 8, "gdn_scan, one token")
+    # the layer's own kernels: the convolution in front of the mixer, the scaled add with the next norm
+    h16 = rnd(T, H, dtype=torch.bfloat16)
+    canon = rnd(H, taps)
+    side = torch.zeros(4, (taps - 1) * H, device=dev)
+    read16 = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    spans, slots = ints(T * r // 4 for r in range(5)), ints(range(4))
+    row_req = ints(r for r in range(4) for _ in range(T // 4))
+    record(f"short_conv added to its input, {T} x {H}, {taps} taps",
+           kernel_time(lambda: ops.short_conv(h16, 0, H, canon, None, side, 0, row_req, spans, slots, read16, residual=True)),
+           T * H * 4, "silu_gate")
+    x, a16, b16 = rnd(T, H), rnd(T, H, dtype=torch.bfloat16), rnd(T, H, dtype=torch.bfloat16)
+    v1, v2, g1 = torch.ones(H, device=dev), torch.ones(H, device=dev), torch.ones(H, device=dev)
+    out16 = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    record(f"scaled_add_norm, two scaled outputs and the next norm, {T} x {H}",
+           kernel_time(lambda: ops.scaled_add_norm(x, [(a16, v1), (b16, v2)], g1, 1e-6, out16)), T * H * (2 + 2 + 4 + 4 + 2),
+           "rms_norm")
+    nh, nkv, d = 16, 4, 128
+    wide = rnd(T, (nh + 2 * nkv) * d)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    req = torch.zeros(T, dtype=torch.int32, device=dev)
+    q_out = torch.empty(T, nh * d, dtype=torch.bfloat16, device=dev)
+    k_pool = torch.zeros(T + 64, nkv, d, dtype=torch.bfloat16, device=dev)
+    v_pool = torch.zeros_like(k_pool)
+    qg, kg, temp = torch.ones(nh * d, device=dev), torch.ones(nkv * d, device=dev), torch.ones(nh, device=dev)
+    record(f"qkv_rotate_store with whole-projection norms and temperatures, {T} tokens, {nh} heads over {nkv} of {d} lanes",
+           kernel_time(lambda: ops.qkv_rotate_store(wide, 0, None, None, 0, pos, pos, req, q_out, k_pool, v_pool, nh, nkv, d, d, d,
+                                                    q_gain=qg, k_gain=kg, eps=1e-6, temp=temp)),
+           T * (nh + 2 * nkv) * d * (4 + 2), "qkv_rotate_store")
+    freq = torch.tensor([1e6 ** (-2.0 * i / 64) for i in range(32)], device=dev)
+    bias = torch.zeros((nh + 2 * nkv) * d, device=dev)
+    record(f"qkv_rotate_store, biases and 64 rotated lanes (Katopel path), {T} tokens",
+           kernel_time(lambda: ops.qkv_rotate_store(wide, 0, bias, freq, 64, pos, pos, req, q_out, k_pool, v_pool, nh, nkv, d, d, d)),
+           T * (nh + 2 * nkv) * d * (4 + 2), None)
+    experts, ff, shared_ff = 8, 512, 1536
+    gu = rnd(T, 2 * I, dtype=torch.bfloat16)
+    share = torch.rand(T, experts + 1, device=dev)
+    act = torch.empty(T, I, dtype=torch.bfloat16, device=dev)
+    record(f"moe_gate, clamped activation, {T} x {I} lanes of {experts} experts and a shared one",
+           kernel_time(lambda: ops.moe_gate(gu, share, act, experts, ff, True, activation="clamped_swish", limit=7.0,
+                                            shared_limit=7.0, alpha=1.702)), T * I * 6, "moe_gate")
+    record(f"moe_gate, silu (Katopel path), {T} x {I}", kernel_time(lambda: ops.moe_gate(gu, share, act, experts, ff, True)),
+           T * I * 6, None)
+    h_in = rnd(T, H, dtype=torch.bfloat16)
+    router, correction = rnd(experts, H), rnd(experts)
+    record(f"moe_route, sigmoid scores, 2 of {experts} experts inside 2 of 4 groups, width {H}",
+           kernel_time(lambda: ops.moe_route(h_in, router, experts, 2, "one", share, score="sigmoid", correction=correction,
+                                             groups=4, keep=2, scale=2.5)), T * H * 2, "moe_route")
+    router9 = rnd(experts + 1, H)
+    record(f"moe_route, softmax of the chosen (Katopel path), width {H}",
+           kernel_time(lambda: ops.moe_route(h_in, router9, experts, 2, True, share)), T * H * 2, None)
+    table16, ptable16 = rnd(32000, H, dtype=torch.bfloat16), rnd(T, H, dtype=torch.bfloat16)
+    ids = torch.randint(0, 32000, (T,), device=dev, dtype=torch.int32)
+    record(f"embed_positions, {T} x {H}", kernel_time(lambda: ops.embed_positions(ids, pos, req, table16, ptable16, x)),
+           T * H * (2 + 2 + 4), "embed")
+    record(f"embed, {T} x {H}", kernel_time(lambda: ops.embed(ids, table16, x)), T * H * (2 + 4), None)
+    # the like kernels of the paths that were there before
+    record(f"silu_gate, {T} x {I}", kernel_time(lambda: ops.silu_gate(gu, act)), T * I * 6, None)
+    record(f"rms_norm with pending add, {T} x {H}", kernel_time(lambda: ops.rms_norm(x, g1, 1e-6, out16, delta=a16)),
+           T * H * (4 + 4 + 2 + 2), None)
+    b1 = torch.zeros(H, device=dev)
+    record(f"post_norm_add with the next norm (Katopel path), {T} x {H}",
+           kernel_time(lambda: ops.post_norm_add(x, [(a16, 1.0)], g1, b1, 1e-6, g1, b1, 1e-6, out16)), T * H * (2 + 4 + 4 + 2), None)
+    # the delta rule at the Katopel 2k size: its prepare, scan and output norm
+    d_heads, d_groups, d_dim, d_vdim = 16, 8, 128, 128
+    d_channels = 2 * d_groups * d_dim + d_heads * d_vdim
+    padded = ops.gdn_padded_dim(d_dim)
+    d_off = d_heads * d_vdim * padded
+    d_slot = -(-(d_off + (taps - 1) * d_channels) // 4) * 4
+    d_proj = rnd(T, d_channels + 2 * d_heads + d_heads * d_vdim)
+    d_conv = rnd(d_channels, taps)
+    qkv, bg = torch.empty(T, d_channels, device=dev), torch.empty(T, 2 * d_heads + d_groups, device=dev)
+    o = torch.empty(T, d_heads * d_vdim, device=dev)
+    o16 = torch.empty(T, d_heads * d_vdim, dtype=torch.bfloat16, device=dev)
+    d_a, d_b = rnd(d_heads), rnd(d_heads)
+    for requests in (1, 4):
+        state = torch.zeros(requests, d_slot, device=dev)
+        spans, slots = ints(T * r // requests for r in range(requests + 1)), ints(range(requests))
+        row_req = ints(r for r in range(requests) for _ in range(T // requests))
+        record(f"gdn_prepare (Katopel path), {T} tokens of {requests} request(s), {d_channels} channels of {taps} taps",
+               kernel_time(lambda: ops.gdn_prepare(d_proj, 0, d_channels, d_channels + d_heads, d_groups, d_heads, d_dim, d_vdim,
+                                                   taps, d_conv, d_a, d_b, state, d_off, row_req, spans, slots, qkv, bg)),
+               T * (d_channels + 2 * d_heads) * 8, None)
+        record(f"gdn_scan (Katopel path), {T} tokens of {requests} request(s), {d_heads} heads of {d_dim} x {d_vdim}",
+               kernel_time(lambda: ops.gdn_scan(qkv, bg, d_groups, d_heads, d_dim, d_vdim, state, spans, slots, o,
+                                                longest=T // requests)),
+               T * (d_channels + 2 * d_heads + d_heads * d_vdim) * 4, None, flops=T * d_heads * d_dim * d_vdim * 8)
+    record(f"gdn_out_norm (Katopel path), {T} tokens x {d_heads} heads of {d_vdim}",
+           kernel_time(lambda: ops.gdn_out_norm(o, d_proj, d_channels + 2 * d_heads, torch.ones(d_vdim, device=dev), 1.0, 1e-6,
+                                                o16, d_heads, d_vdim, row_req)), T * d_heads * d_vdim * (4 + 4 + 2), None)
+    state = torch.zeros(rows, d_slot, device=dev)
+    spans, slots = ints(range(rows + 1)), ints(range(rows))
+    record(f"gdn_scan (Katopel path), {rows} requests of one token",
+           kernel_time(lambda: ops.gdn_scan(qkv[:rows], bg[:rows], d_groups, d_heads, d_dim, d_vdim, state, spans, slots, o[:rows])),
+           rows * d_off * 8, None)
+    ops.raise_if_error()
+    print(json.dumps({
+        "metric": "prefill and decode tok/s of the Vizonex design beside Katopel at equal width, depth and parameters",
+        "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup, "dtype": "bf16",
+        "data": "synthetic: random weights drawn on the device, uniform random token ids",
+        "config": {"sizes": VIZONEX_SIZES, "prefill_tokens": PREFILL_TOKENS, "decode_context": context,
                    "peaks": pk["source"], "hbm_gbs": pk["hbm_gbs"],
                    "l2": "kernels alone: inputs larger than L2 and a 256 MB write between timed launches"},
         "models": models, "kernels": kernels}))
