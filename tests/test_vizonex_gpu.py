@@ -79,10 +79,13 @@ def test_short_convolution_over_portions_gives_what_the_whole_sequences_give(cha
     step = 0
     while any(d < n for d, n in zip(done, lengths)):
         take = [min(sizes[(step + r) % len(sizes)], n - d) for r, (d, n) in enumerate(zip(done, lengths))]
+        if step % 3 == 0:
+            take = [min(1, t) for t in take]              # a step of single tokens: the kept inputs move in the same launch
         live = [r for r in range(3) if take[r] and (step + r) % 4 != 3]      # a request sits out now and then
         if not live:
             step += 1
             continue
+        single = all(take[r] == 1 for r in live)
         rows = torch.cat([xs[r][done[r]:done[r] + take[r]] for r in live])
         rows = torch.cat([rows, torch.full((2, rows.shape[1]), float("nan"), dtype=dtype, device=DEV)])   # padding rows
         row_req, q_start = batch_of([take[r] for r in live])
@@ -90,8 +93,9 @@ def test_short_convolution_over_portions_gives_what_the_whole_sequences_give(cha
         out = torch.full((rows.shape[0], channels), float("nan"), device=DEV)
         slot_of = ints([slots[r] for r in live])
         o.short_conv(rows, extra, channels, w, b, state, off, row_req, q_start, slot_of, out, activation=activation,
-                     residual=residual)
-        o.short_conv_state(rows, extra, channels, taps, state, off, q_start, slot_of)
+                     residual=residual, shift=single)
+        if not single:
+            o.short_conv_state(rows, extra, channels, taps, state, off, q_start, slot_of)
         at = 0
         for r in live:
             got[r][done[r]:done[r] + take[r]] = out[at:at + take[r]]
@@ -106,8 +110,37 @@ def test_short_convolution_over_portions_gives_what_the_whole_sequences_give(cha
         close(kept, xs[2][-(taps - 1):, extra:], torch.float32, "kept inputs", tol=0.0 if dtype == torch.float32 else 1e-6)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("channels,taps", [(320, 4), (72, 2), (128, 3), (50, 3)])
+def test_short_convolution_in_steps_of_thousands_of_rows(channels, taps, dtype):
+    """Steps of 2,437 and of 360 rows (the kernel's runs of rows begin inside requests and straddle their borders),
+    then one of single tokens."""
+    o = ops()
+    lengths, slots = [1100 + 120 + 1, 37 + 120 + 1, 1300 + 120 + 1], [1, 2, 0]
+    xs = [rnd(n, channels, seed=25 + i, dtype=dtype) for i, n in enumerate(lengths)]
+    w, b = rnd(channels, taps, seed=28, scale=0.6), rnd(channels, seed=29)
+    state = torch.zeros(3, (taps - 1) * channels, device=DEV)
+    want = [plain.silu(plain.causal_convolution(x.double().cpu(), w.double().cpu(), b.double().cpu())) for x in xs]
+    done = [0, 0, 0]
+    for take in ([1100, 37, 1300], [120, 120, 120], [1, 1, 1]):
+        rows = torch.cat([xs[r][done[r]:done[r] + take[r]] for r in range(3)])
+        row_req, q_start = batch_of(take)
+        out = torch.full((rows.shape[0], channels), float("nan"), dtype=dtype, device=DEV)
+        single = take == [1, 1, 1]
+        o.short_conv(rows, 0, channels, w, b, state, 0, row_req, q_start, ints(slots), out, activation="silu", shift=single)
+        if not single:
+            o.short_conv_state(rows, 0, channels, taps, state, 0, q_start, ints(slots))
+        at = 0
+        for r in range(3):
+            close(out[at:at + take[r]], want[r][done[r]:done[r] + take[r]], dtype, f"request {r}")
+            at += take[r]
+            done[r] += take[r]
+    kept = state[slots[1]].view(taps - 1, channels)
+    close(kept, xs[1][-(taps - 1):], torch.float32, "kept inputs", tol=0.0 if dtype == torch.float32 else 1e-6)
+
+
 # ---- both sublayers' outputs, each scaled by its vector, added; the norm behind -------------------------
-@pytest.mark.parametrize("width", [50, 320, 2048, 9001])
+@pytest.mark.parametrize("width", [50, 320, 2048, 8192, 9001])
 @pytest.mark.parametrize("form", ["one bf16", "two bf16", "f32 and partials"])
 def test_scaled_outputs_are_added_and_the_sum_is_normed(width, form):
     o = ops()

@@ -4,12 +4,15 @@
 //     dt = softplus(raw_dt + dt_bias);  S <- exp(-exp(A_log) dt) S + dt B x^T;  y = S^T C + D x
 // with x (P lanes of the head), B and C (N lanes of the head's group) the convolved and activated
 // inputs.  The columns of S are independent (column p needs x_p only), so thread (column p, part j)
-// keeps the rows j, j + 8, j + 16, ... of column p in registers; the 8 parts of a column add their
-// shares of S^T C in one round of shuffles.
+// keeps NPER neighbouring rows of column p in registers (rows j NPER .. (j + 1) NPER - 1); the 8 parts
+// of a column add their shares of S^T C in one round of shuffles.
 //
-//   mamba2_scan      the recurrence over every request's rows of the step, token by token; tokens are
-//                    staged through shared memory in runs.  Grid: (blocks of 32 columns, heads,
-//                    requests).  State: [slots, stride], a slot's matrices [heads, P, N] at its start.
+//   mamba2_scan      the recurrence over every request's rows of the step, token by token.  Tokens are
+//                    staged through shared memory in runs (cp.async, the next run on its way while
+//                    the current one is computed); a part's rows of B and C lie side by side there,
+//                    padded so that the 16-byte reads of the 8 parts fall on different banks.  Grid:
+//                    (blocks of 32 columns, heads, requests).  State: [slots, stride], a slot's
+//                    matrices [heads, P, N] at its start.
 //   mamba2_out_norm  y * silu(z), divided by its root mean square inside each of `parts` equal parts
 //                    of the row, times a gain: a block a (row, part).
 #include "common.cuh"
@@ -17,9 +20,18 @@
 #define M2_PARTS 8                 // threads that share a column
 #define M2_COLS 32                 // columns a block
 #define M2_THREADS (M2_PARTS * M2_COLS)
-#define M2_RUN 16                  // tokens staged at a time
 
 __device__ __forceinline__ float m2_softplus(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+
+__device__ __forceinline__ void m2_copy4(float* dst, const float* src) {
+  const unsigned to = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(to), "l"(src) : "memory");
+}
+
+__device__ __forceinline__ void m2_copy16(float* dst, const float* src) {
+  const unsigned to = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(to), "l"(src) : "memory");
+}
 
 // xbc: float32 [T, channels]: x (heads * P), B (groups * N), C (groups * N).  proj: the input product
 // [T, ld] whose columns dt_at .. + heads are the raw step sizes.
@@ -29,67 +41,143 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __rest
                    const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ skip,
                    int heads, int groups, int P, int N, float* __restrict__ state, long long stride,
                    const int* __restrict__ q_start, const int* __restrict__ state_slot, float* __restrict__ y) {
-  constexpr int NPAD = NPER * M2_PARTS;
-  __shared__ float Bs[M2_RUN][NPAD];
-  __shared__ float Cs[M2_RUN][NPAD];
-  __shared__ float xs[M2_RUN][M2_COLS];
-  __shared__ float dts[M2_RUN];
-  __shared__ float decs[M2_RUN];
+  constexpr int RUN = NPER >= 32 ? 8 : 16;            // tokens staged at a time
+  constexpr int PADDED = NPER + 4;                    // a part's rows and four idle lanes
+  constexpr int NPAD = PADDED * M2_PARTS;
+  __shared__ __align__(16) float Bs[2][RUN][NPAD];
+  __shared__ __align__(16) float Cs[2][RUN][NPAD];
+  __shared__ __align__(16) float xs[2][RUN][M2_COLS];
+  __shared__ float dts[2][RUN];
+  __shared__ float decs[2][RUN];
   const int head = blockIdx.y, r = blockIdx.z;
   const int col0 = blockIdx.x * M2_COLS;
   const int part = threadIdx.x % M2_PARTS, col = col0 + threadIdx.x / M2_PARTS;
   const int group = head / (heads / groups);
   const int inner = heads * P;
   const float a = expf(a_log[head]), bias = dt_bias[head], d = skip[head];
+  // lanes that no copy reaches (rows from N on, columns from P on) stay zero in both halves
+  if (N < NPER * M2_PARTS) {
+    for (int i = threadIdx.x; i < 2 * RUN * NPAD; i += M2_THREADS) {
+      (&Bs[0][0][0])[i] = 0.f;
+      (&Cs[0][0][0])[i] = 0.f;
+    }
+  }
+  if (P - col0 < M2_COLS)
+    for (int i = threadIdx.x; i < 2 * RUN * M2_COLS; i += M2_THREADS) (&xs[0][0][0])[i] = 0.f;
   pdl_wait();
   pdl_launch();
   const int first = q_start[r], n = q_start[r + 1] - first;
   if (n <= 0) return;
   float* mine = state + (size_t)state_slot[r] * stride + ((size_t)head * P + col) * N;
   float S[NPER];
+  // a thread's rows are neighbours in the slot: 16-byte loads where the matrix has whole runs of them
+  const bool whole = N == NPER * M2_PARTS && col < P && (stride & 3) == 0 && ((uintptr_t)state & 15) == 0;
+  if (whole) {
 #pragma unroll
-  for (int i = 0; i < NPER; ++i) {
-    const int row = i * M2_PARTS + part;
-    S[i] = (col < P && row < N) ? mine[row] : 0.f;
+    for (int i = 0; i < NPER / 4; ++i) {
+      const float4 v = *reinterpret_cast<const float4*>(mine + part * NPER + 4 * i);
+      S[4 * i] = v.x; S[4 * i + 1] = v.y; S[4 * i + 2] = v.z; S[4 * i + 3] = v.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < NPER; ++i) {
+      const int row = part * NPER + i;
+      S[i] = (col < P && row < N) ? mine[row] : 0.f;
+    }
   }
-  for (int run = 0; run < n; run += M2_RUN) {
-    const int here = n - run < M2_RUN ? n - run : M2_RUN;
-    __syncthreads();                       // the run before is read to its end
-    for (int i = threadIdx.x; i < here * NPAD; i += M2_THREADS) {
-      const int k = i / NPAD, row = i % NPAD;
-      const float* src = xbc + (size_t)(first + run + k) * channels + inner + group * N;
-      Bs[k][row] = row < N ? src[row] : 0.f;
-      Cs[k][row] = row < N ? src[(size_t)groups * N + row] : 0.f;
+  __syncthreads();                         // the zeros are written before the first copies land
+  // 16 bytes a copy where rows, lanes and channels come in whole 4s (a piece of 4 rows lies inside one part)
+  const bool by16 = ((N | P | channels) & 3) == 0 && ((uintptr_t)xbc & 15) == 0;
+  auto stage = [&](int run, int half) {    // the copies of a run's x, B and C, in flight when it returns
+    const int here = n - run < RUN ? n - run : RUN;
+    const int cols = P - col0 < M2_COLS ? P - col0 : M2_COLS;
+    if (by16) {
+      const int pieces = N >> 2;
+      for (int i = threadIdx.x; i < here * pieces; i += M2_THREADS) {
+        const int k = i / pieces, row = (i - k * pieces) << 2;
+        const float* src = xbc + (size_t)(first + run + k) * channels + inner + group * N + row;
+        const int at = (row / NPER) * PADDED + row % NPER;
+        m2_copy16(&Bs[half][k][at], src);
+        m2_copy16(&Cs[half][k][at], src + (size_t)groups * N);
+      }
+      const int across = cols >> 2;
+      for (int i = threadIdx.x; i < here * across; i += M2_THREADS) {
+        const int k = i / across, c = (i - k * across) << 2;
+        m2_copy16(&xs[half][k][c], xbc + (size_t)(first + run + k) * channels + head * P + col0 + c);
+      }
+    } else {
+      for (int i = threadIdx.x; i < here * N; i += M2_THREADS) {
+        const int k = i / N, row = i - k * N;
+        const float* src = xbc + (size_t)(first + run + k) * channels + inner + group * N + row;
+        const int at = (row / NPER) * PADDED + row % NPER;
+        m2_copy4(&Bs[half][k][at], src);
+        m2_copy4(&Cs[half][k][at], src + (size_t)groups * N);
+      }
+      for (int i = threadIdx.x; i < here * cols; i += M2_THREADS) {
+        const int k = i / cols, c = i - k * cols;
+        m2_copy4(&xs[half][k][c], xbc + (size_t)(first + run + k) * channels + head * P + col0 + c);
+      }
     }
-    for (int i = threadIdx.x; i < here * M2_COLS; i += M2_THREADS) {
-      const int k = i / M2_COLS, c = col0 + i % M2_COLS;
-      xs[k][i % M2_COLS] = c < P ? xbc[(size_t)(first + run + k) * channels + head * P + c] : 0.f;
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  auto raw_step = [&](int run) {           // the raw step size of token run + threadIdx.x (asked for early)
+    return threadIdx.x < RUN && run + (int)threadIdx.x < n
+               ? to_float(proj[(size_t)(first + run + threadIdx.x) * ld + dt_at + head]) : 0.f;
+  };
+  auto keep_step = [&](float raw, int half) {
+    if (threadIdx.x < RUN) {
+      const float dt = m2_softplus(raw + bias);
+      dts[half][threadIdx.x] = dt;
+      decs[half][threadIdx.x] = expf(-a * dt);
     }
-    if (threadIdx.x < here) {
-      const float dt = m2_softplus(to_float(proj[(size_t)(first + run + threadIdx.x) * ld + dt_at + head]) + bias);
-      dts[threadIdx.x] = dt;
-      decs[threadIdx.x] = expf(-a * dt);
+  };
+  stage(0, 0);
+  keep_step(raw_step(0), 0);
+  int half = 0;
+  for (int run = 0; run < n; run += RUN, half ^= 1) {
+    const int here = n - run < RUN ? n - run : RUN;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                       // this run has landed; the other half has been read to its end
+    const bool more = run + RUN < n;
+    float raw = 0.f;
+    if (more) {
+      stage(run + RUN, half ^ 1);
+      raw = raw_step(run + RUN);
     }
-    __syncthreads();
     for (int k = 0; k < here; ++k) {
-      const float x = xs[k][threadIdx.x / M2_PARTS];
-      const float dec = decs[k], dtx = dts[k] * x;
+      const float x = xs[half][k][threadIdx.x / M2_PARTS];
+      const float dec = decs[half][k], dtx = dts[half][k] * x;
+      const float4* b4 = reinterpret_cast<const float4*>(&Bs[half][k][part * PADDED]);
+      const float4* c4 = reinterpret_cast<const float4*>(&Cs[half][k][part * PADDED]);
       float acc = 0.f;
 #pragma unroll
-      for (int i = 0; i < NPER; ++i) {
-        const int row = i * M2_PARTS + part;
-        S[i] = fmaf(dec, S[i], dtx * Bs[k][row]);
-        acc = fmaf(S[i], Cs[k][row], acc);
+      for (int i = 0; i < NPER / 4; ++i) {
+        const float4 b = b4[i], c = c4[i];
+        S[4 * i] = fmaf(dec, S[4 * i], dtx * b.x);
+        S[4 * i + 1] = fmaf(dec, S[4 * i + 1], dtx * b.y);
+        S[4 * i + 2] = fmaf(dec, S[4 * i + 2], dtx * b.z);
+        S[4 * i + 3] = fmaf(dec, S[4 * i + 3], dtx * b.w);
+        acc = fmaf(S[4 * i], c.x, acc);
+        acc = fmaf(S[4 * i + 1], c.y, acc);
+        acc = fmaf(S[4 * i + 2], c.z, acc);
+        acc = fmaf(S[4 * i + 3], c.w, acc);
       }
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);
       acc += __shfl_xor_sync(0xffffffffu, acc, 4);
       if (part == 0 && col < P) y[(size_t)(first + run + k) * inner + head * P + col] = fmaf(d, x, acc);
     }
+    if (more) keep_step(raw, half ^ 1);
+  }
+  if (whole) {
+#pragma unroll
+    for (int i = 0; i < NPER / 4; ++i)
+      *reinterpret_cast<float4*>(mine + part * NPER + 4 * i) = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+    return;
   }
 #pragma unroll
   for (int i = 0; i < NPER; ++i) {
-    const int row = i * M2_PARTS + part;
+    const int row = part * NPER + i;
     if (col < P && row < N) mine[row] = S[i];
   }
 }
@@ -166,15 +254,91 @@ mamba2_out_norm_kernel(const float* __restrict__ y, const TI* __restrict__ proj,
   }
 }
 
+
+// Four neighbouring lanes of the gate's pre-activation.
+__device__ __forceinline__ float4 m2_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 m2_load4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void m2_store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void m2_store4(__nv_bfloat16* p, float4 v) {
+  uint2 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+  h[0] = __floats2bfloat162_rn(v.x, v.y);
+  h[1] = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+__device__ __forceinline__ float m2_silu(float z) { return z / (1.0f + expf(-z)); }
+
+// The same for parts of whole 4s up to 2,048 lanes, everything aligned: four lanes a load, the part kept in
+// registers between the sum and the scaling.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+mamba2_out_norm4_kernel(const float* __restrict__ y, const TI* __restrict__ proj, int ld, int z_at,
+                        const float* __restrict__ gain, float eps, int inner, int parts,
+                        const int* __restrict__ row_req, TO* __restrict__ out) {
+  __shared__ float scratch[33];
+  const int t = blockIdx.x, g = blockIdx.y;
+  const int width = inner / parts;
+  pdl_wait();
+  pdl_launch();
+  if (row_req[t] < 0) return;
+  const float* yr = y + (size_t)t * inner + (size_t)g * width;
+  const TI* zr = proj + (size_t)t * ld + z_at + (size_t)g * width;
+  float4 kept[2];
+  float squares = 0.f;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int i = (threadIdx.x + k * blockDim.x) * 4;
+    kept[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < width) {
+      const float4 v = m2_load4(yr + i), z = m2_load4(zr + i);
+      kept[k] = make_float4(v.x * m2_silu(z.x), v.y * m2_silu(z.y), v.z * m2_silu(z.z), v.w * m2_silu(z.w));
+      squares = fmaf(kept[k].x, kept[k].x, squares);
+      squares = fmaf(kept[k].y, kept[k].y, squares);
+      squares = fmaf(kept[k].z, kept[k].z, squares);
+      squares = fmaf(kept[k].w, kept[k].w, squares);
+    }
+  }
+  const float inv = 1.0f / sqrtf(block_sum(squares, scratch) / (float)width + eps);
+  TO* o = out + (size_t)t * inner + (size_t)g * width;
+  const float* gr = gain + (size_t)g * width;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int i = (threadIdx.x + k * blockDim.x) * 4;
+    if (i < width) {
+      const float4 w = m2_load4(gr + i);
+      m2_store4(o + i, make_float4(kept[k].x * inv * w.x, kept[k].y * inv * w.y, kept[k].z * inv * w.z, kept[k].w * inv * w.w));
+    }
+  }
+}
+
 TOKB200_API int tokb200_mamba2_out_norm(const float* y, const void* proj, int proj_dtype, int ld, int z_at,
                                         const float* gain, float eps, int inner, int parts, const int* row_req,
                                         void* out, int out_dtype, int n_rows, cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
   if (inner <= 0 || parts <= 0 || inner % parts || parts > 65535) return TOKB200_BAD_SIZE;
   const int width = inner / parts;
+  const dim3 grid(n_rows, parts);
+  const int z_size = proj_dtype == TOKB200_BF16 ? 2 : 4, o_size = out_dtype == TOKB200_BF16 ? 2 : 4;
+  if (width % 4 == 0 && width <= 2048 && ld % 4 == 0 && z_at % 4 == 0 && (((uintptr_t)y | (uintptr_t)gain) & 15) == 0 &&
+      ((uintptr_t)proj % (4 * z_size)) == 0 && ((uintptr_t)out % (4 * o_size)) == 0) {
+    int threads4 = (width / 4 + 31) / 32 * 32;
+    threads4 = threads4 > 256 ? 256 : threads4;
+#define LAUNCH4(TI, TO)                                                                                              \
+    return launch_dependent(mamba2_out_norm4_kernel<TI, TO>, grid, dim3(threads4), 0, stream, y, (const TI*)proj, ld, \
+                            z_at, gain, eps, inner, parts, row_req, (TO*)out)
+    if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_F32) LAUNCH4(float, float);
+    if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_BF16) LAUNCH4(float, __nv_bfloat16);
+    if (proj_dtype == TOKB200_BF16 && out_dtype == TOKB200_BF16) LAUNCH4(__nv_bfloat16, __nv_bfloat16);
+    if (proj_dtype == TOKB200_BF16 && out_dtype == TOKB200_F32) LAUNCH4(__nv_bfloat16, float);
+#undef LAUNCH4
+  }
   int threads = (width + 31) / 32 * 32;
   threads = threads > 256 ? 256 : threads;
-  const dim3 grid(n_rows, parts);
 #define LAUNCH(TI, TO)                                                                                           \
   return launch_dependent(mamba2_out_norm_kernel<TI, TO>, grid, dim3(threads), 0, stream, y, (const TI*)proj, ld, \
                           z_at, gain, eps, inner, parts, row_req, (TO*)out)

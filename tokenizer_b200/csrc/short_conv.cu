@@ -4,7 +4,9 @@
 //   short_conv        y[t, c] = f(sum_j w[c, j] * x[t - (taps - 1) + j, c] + bias[c]) (+ x[t, c] with
 //                     `residual`), f the identity or silu; inputs before a request's first row of the
 //                     step come from the taps - 1 inputs kept in its state slot (zeros at a
-//                     sequence's start, because a slot starts zeroed).  A block a row.
+//                     sequence's start, because a slot starts zeroed).  A block a row.  With `shift`
+//                     (every request of the step brings ONE row) the row's block also moves the
+//                     request's kept inputs on, which spares the launch below.
 //   short_conv_state  the kept inputs move on by the step's rows (a thread a request and channel);
 //                     launched behind short_conv, which reads the old ones.
 //   scaled_add_norm   x += v1 * a (+ v2 * b), v float32 vectors over the width (a layer's learned
@@ -23,16 +25,16 @@ enum : int { CONV_ACT_NONE = 0, CONV_ACT_SILU = 1 };
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 short_conv_kernel(const TI* __restrict__ x, int ld, int at, int channels, int taps, const float* __restrict__ w,
-                  const float* __restrict__ bias, const float* __restrict__ state, long long stride, int off,
+                  const float* __restrict__ bias, float* state, long long stride, int off,
                   const int* __restrict__ row_req, const int* __restrict__ q_start,
-                  const int* __restrict__ state_slot, int act, int residual, TO* __restrict__ y) {
+                  const int* __restrict__ state_slot, int act, int residual, TO* __restrict__ y, int shift) {
   const int t = blockIdx.x;
   const int r = row_req[t];
   pdl_wait();
   pdl_launch();
   if (r < 0) return;
   const int place = t - q_start[r];                   // the row's place in its request's portion
-  const float* kept = taps > 1 ? state + (size_t)state_slot[r] * stride + off : nullptr;
+  float* kept = taps > 1 ? state + (size_t)state_slot[r] * stride + off : nullptr;
   for (int c = threadIdx.x; c < channels; c += blockDim.x) {
     float acc = bias ? bias[c] : 0.f;
     float now = 0.f;
@@ -50,6 +52,109 @@ short_conv_kernel(const TI* __restrict__ x, int ld, int at, int channels, int ta
     if (act == CONV_ACT_SILU) acc = acc / (1.0f + expf(-acc));
     if (residual) acc += now;
     y[(size_t)t * channels + c] = from_float<TO>(acc);
+    if (shift && taps > 1) {                          // the only row of its request: nobody else reads these
+      for (int k = 0; k + 2 < taps; ++k) kept[(size_t)k * channels + c] = kept[(size_t)(k + 1) * channels + c];
+      kept[(size_t)(taps - 2) * channels + c] = now;
+    }
+  }
+}
+
+
+// Four consecutive channels of a row (8 bytes of bfloat16, 16 of float32).
+__device__ __forceinline__ float4 conv_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 conv_load4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void conv_store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void conv_store4(__nv_bfloat16* p, float4 v) {
+  uint2 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+  h[0] = __floats2bfloat162_rn(v.x, v.y);
+  h[1] = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// The same convolution for 2 to 4 taps and channels in whole 4s: a thread owns four neighbouring channels over
+// `rows` consecutive rows of the step and keeps the last TAPS - 1 inputs in registers, so that every input is
+// loaded once; where a row starts a request's portion (or the thread's run) the window is filled from the
+// rows before it and the inputs kept in the request's slot.  Sums in the order of the kernel above.
+template <int TAPS, int ROWS, typename TI, typename TO>
+__global__ void __launch_bounds__(128)
+short_conv_tile_kernel(const TI* __restrict__ x, int ld, int at, int channels, const float* __restrict__ w,
+                       const float* __restrict__ bias, float* state, long long stride, int off,
+                       const int* __restrict__ row_req, const int* __restrict__ q_start,
+                       const int* __restrict__ state_slot, int act, int residual, TO* __restrict__ y, int shift,
+                       int n_rows) {
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  const int t0 = blockIdx.x * ROWS;
+  pdl_wait();
+  pdl_launch();
+  if (c >= channels) return;
+  float wt[4][TAPS];
+#pragma unroll
+  for (int v = 0; v < 4; ++v)
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) wt[v][j] = w[(size_t)(c + v) * TAPS + j];
+  const float4 b4 = bias ? *reinterpret_cast<const float4*>(bias + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 win[TAPS - 1];                               // win[k]: the input TAPS - 1 - k rows before the current one
+  int before = -2;
+  // the run's own inputs are asked for at once (the rows exist whoever they belong to)
+  float4 in[ROWS];
+  int owner[ROWS], begin[ROWS];                       // and so is whose they are and where those portions start
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) {
+    in[i] = t0 + i < n_rows ? conv_load4(x + (size_t)(t0 + i) * ld + at + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    owner[i] = t0 + i < n_rows ? row_req[t0 + i] : -1;
+  }
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) begin[i] = owner[i] >= 0 ? q_start[owner[i]] : 0;
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) {
+    const int t = t0 + i;
+    if (t >= n_rows) break;
+    const int r = owner[i];
+    if (r < 0) { before = -2; continue; }
+    const int place = t - begin[i];
+    float* kept = nullptr;
+    if (r != before || place == 0 || shift) kept = state + (size_t)state_slot[r] * stride + off;
+    if (r != before || place == 0) {
+#pragma unroll
+      for (int k = 0; k < TAPS - 1; ++k) {
+        const int back = TAPS - 1 - k;
+        win[k] = back <= place ? conv_load4(x + (size_t)(t - back) * ld + at + c)
+                               : *reinterpret_cast<const float4*>(kept + (size_t)(TAPS - 1 - (back - place)) * channels + c);
+      }
+    }
+    before = r;
+    const float4 now = in[i];
+    float acc[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+    for (int k = 0; k < TAPS - 1; ++k) {
+      acc[0] = fmaf(wt[0][k], win[k].x, acc[0]);
+      acc[1] = fmaf(wt[1][k], win[k].y, acc[1]);
+      acc[2] = fmaf(wt[2][k], win[k].z, acc[2]);
+      acc[3] = fmaf(wt[3][k], win[k].w, acc[3]);
+    }
+    acc[0] = fmaf(wt[0][TAPS - 1], now.x, acc[0]);
+    acc[1] = fmaf(wt[1][TAPS - 1], now.y, acc[1]);
+    acc[2] = fmaf(wt[2][TAPS - 1], now.z, acc[2]);
+    acc[3] = fmaf(wt[3][TAPS - 1], now.w, acc[3]);
+    if (act == CONV_ACT_SILU) {
+#pragma unroll
+      for (int v = 0; v < 4; ++v) acc[v] = acc[v] / (1.0f + expf(-acc[v]));
+    }
+    if (residual) { acc[0] += now.x; acc[1] += now.y; acc[2] += now.z; acc[3] += now.w; }
+    conv_store4(y + (size_t)t * channels + c, make_float4(acc[0], acc[1], acc[2], acc[3]));
+#pragma unroll
+    for (int k = 0; k + 2 < TAPS; ++k) win[k] = win[k + 1];
+    win[TAPS - 2] = now;
+    if (shift) {                                      // the only row of its request: its kept inputs move on here
+#pragma unroll
+      for (int k = 0; k < TAPS - 1; ++k) *reinterpret_cast<float4*>(kept + (size_t)k * channels + c) = win[k];
+    }
   }
 }
 
@@ -79,17 +184,41 @@ __global__ void short_conv_state_kernel(const TI* __restrict__ x, int ld, int at
 }
 
 TOKB200_API int tokb200_short_conv(const void* x, int x_dtype, int ld, int at, int channels, int taps, const float* w,
-                                   const float* bias, const float* state, long long stride, int off,
+                                   const float* bias, float* state, long long stride, int off,
                                    const int* row_req, const int* q_start, const int* state_slot, int act,
-                                   int residual, void* y, int y_dtype, int n_rows, cudaStream_t stream) {
+                                   int residual, void* y, int y_dtype, int n_rows, int shift, cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
   if (channels <= 0 || taps < 1 || taps > CONV_MAX_TAPS || (act != CONV_ACT_NONE && act != CONV_ACT_SILU) ||
       (taps > 1 && (state == nullptr || off < 0 || off + (long long)(taps - 1) * channels > stride)))
     return TOKB200_BAD_SIZE;
+  const int x_size = x_dtype == TOKB200_BF16 ? 2 : 4, y_size = y_dtype == TOKB200_BF16 ? 2 : 4;
+  if (taps >= 2 && taps <= 4 && channels % 4 == 0 && at % 4 == 0 && ld % 4 == 0 && off % 4 == 0 && stride % 4 == 0 &&
+      ((uintptr_t)x % (4 * x_size)) == 0 && ((uintptr_t)y % (4 * y_size)) == 0 &&
+      (((uintptr_t)state | (uintptr_t)bias) & 15) == 0) {
+    // many rows: runs of 8 rows a thread; few (a decoding step): a row a thread, so that the blocks are many
+    const int rows = n_rows >= 1024 ? 8 : 1;
+    const int threads = channels / 4 >= 128 ? 128 : (channels / 4 + 31) / 32 * 32;
+    const dim3 grid((n_rows + rows - 1) / rows, (channels / 4 + threads - 1) / threads);
+#define TILE(TAPS, ROWS, TI, TO)                                                                                     \
+    return launch_dependent(short_conv_tile_kernel<TAPS, ROWS, TI, TO>, grid, dim3(threads), 0, stream, (const TI*)x, \
+                            ld, at, channels, w, bias, state, stride, off, row_req, q_start, state_slot, act,         \
+                            residual, (TO*)y, shift, n_rows)
+#define TILE_BY_TAPS(TI, TO)                                                    \
+    if (taps == 2) { if (rows == 8) TILE(2, 8, TI, TO); TILE(2, 1, TI, TO); }   \
+    if (taps == 3) { if (rows == 8) TILE(3, 8, TI, TO); TILE(3, 1, TI, TO); }   \
+    if (rows == 8) TILE(4, 8, TI, TO);                                          \
+    TILE(4, 1, TI, TO)
+    if (grid.y <= 65535) {                  // the pairs of types that the layers use; the others take the kernel above
+      if (x_dtype == TOKB200_F32 && y_dtype == TOKB200_F32) { TILE_BY_TAPS(float, float); }
+      if (x_dtype == TOKB200_BF16 && y_dtype == TOKB200_BF16) { TILE_BY_TAPS(__nv_bfloat16, __nv_bfloat16); }
+    }
+#undef TILE_BY_TAPS
+#undef TILE
+  }
 #define LAUNCH(TI, TO)                                                                                            \
   return launch_dependent(short_conv_kernel<TI, TO>, dim3(n_rows), dim3(256), 0, stream, (const TI*)x, ld, at,   \
                           channels, taps, w, bias, state, stride, off, row_req, q_start, state_slot, act,       \
-                          residual, (TO*)y)
+                          residual, (TO*)y, shift)
   if (x_dtype == TOKB200_F32 && y_dtype == TOKB200_F32) LAUNCH(float, float);
   if (x_dtype == TOKB200_F32 && y_dtype == TOKB200_BF16) LAUNCH(float, __nv_bfloat16);
   if (x_dtype == TOKB200_BF16 && y_dtype == TOKB200_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -169,10 +298,107 @@ scaled_add_norm_kernel(float* __restrict__ x, const TA* __restrict__ a, int a_pa
     y[base + i] = from_float<TO>(x[base + i] * inv * gain[i]);
 }
 
+
+__device__ __forceinline__ void store8(float* out, const float* v) {
+  *reinterpret_cast<float4*>(out) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(out + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* out, const float* v) {
+  uint4 packed;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+  *reinterpret_cast<uint4*>(out) = packed;
+}
+
+// Eight consecutive elements of a term (16 bytes of bfloat16; float32 planes added in index order).
+__device__ __forceinline__ void san_load8(const __nv_bfloat16* __restrict__ y, int, size_t, size_t i, float* v) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(y + i);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = __bfloat1622float2(h[e]);
+    v[2 * e] = f.x;
+    v[2 * e + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void san_load8(const float* __restrict__ y, int n_partials, size_t stride, size_t i, float* v) {
+#pragma unroll
+  for (int e = 0; e < 8; ++e) v[e] = 0.f;
+  for (int s = 0; s < n_partials; ++s) {
+    const float4 lo = *reinterpret_cast<const float4*>(y + i + (size_t)s * stride);
+    const float4 hi = *reinterpret_cast<const float4*>(y + i + (size_t)s * stride + 4);
+    v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w; v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
+  }
+}
+
+// Widths in whole 8s up to 8,192, everything 16-byte aligned: eight elements a thread with 16-byte loads,
+// the row kept in registers between the sum and the scaling.
+template <typename TA, typename TB, typename TO>
+__global__ void __launch_bounds__(1024)
+scaled_add_norm_rows_kernel(float* __restrict__ x, const TA* __restrict__ a, int a_partials, size_t a_stride,
+                            const float* __restrict__ va, const TB* __restrict__ b, int b_partials, size_t b_stride,
+                            const float* __restrict__ vb, const float* __restrict__ gain, float eps,
+                            TO* __restrict__ y, int hidden) {
+  __shared__ float scratch[33];
+  pdl_wait();
+  pdl_launch();
+  const size_t base = (size_t)blockIdx.x * hidden;
+  const int c = threadIdx.x * 8;
+  const bool on = c < hidden;
+  float v[8];
+  float squares = 0.f;
+  if (on) {
+    const float4 x0 = *reinterpret_cast<const float4*>(x + base + c);
+    const float4 x1 = *reinterpret_cast<const float4*>(x + base + c + 4);
+    v[0] = x0.x; v[1] = x0.y; v[2] = x0.z; v[3] = x0.w; v[4] = x1.x; v[5] = x1.y; v[6] = x1.z; v[7] = x1.w;
+    float t[8], s[8];
+    san_load8(a, a_partials, a_stride, base + c, t);
+    *reinterpret_cast<float4*>(s) = *reinterpret_cast<const float4*>(va + c);
+    *reinterpret_cast<float4*>(s + 4) = *reinterpret_cast<const float4*>(va + c + 4);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = fmaf(s[e], t[e], v[e]);
+    if (b != nullptr) {
+      san_load8(b, b_partials, b_stride, base + c, t);
+      *reinterpret_cast<float4*>(s) = *reinterpret_cast<const float4*>(vb + c);
+      *reinterpret_cast<float4*>(s + 4) = *reinterpret_cast<const float4*>(vb + c + 4);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = fmaf(s[e], t[e], v[e]);
+    }
+    *reinterpret_cast<float4*>(x + base + c) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(x + base + c + 4) = make_float4(v[4], v[5], v[6], v[7]);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) squares = fmaf(v[e], v[e], squares);
+  }
+  if (gain == nullptr) return;
+  const float inv = 1.0f / sqrtf(block_sum(squares, scratch) / (float)hidden + eps);
+  if (on) {
+    float g[8];
+    *reinterpret_cast<float4*>(g) = *reinterpret_cast<const float4*>(gain + c);
+    *reinterpret_cast<float4*>(g + 4) = *reinterpret_cast<const float4*>(gain + c + 4);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = v[e] * inv * g[e];
+    store8(y + base + c, v);
+  }
+}
+
 template <typename TA, typename TB>
 static int scaled_add_norm_out(float* x, const void* a, int a_partials, long long a_stride, const float* va,
                                const void* b, int b_partials, long long b_stride, const float* vb, const float* gain,
                                float eps, void* y, int y_dtype, int n_rows, int hidden, cudaStream_t stream) {
+  const int y_size = y_dtype == TOKB200_BF16 ? 2 : 4;
+  if (hidden % 8 == 0 && hidden <= 8192 && a_stride % 4 == 0 && b_stride % 4 == 0 &&
+      (((uintptr_t)x | (uintptr_t)a | (uintptr_t)b | (uintptr_t)va | (uintptr_t)vb | (uintptr_t)gain | (uintptr_t)y) & 15) == 0 &&
+      ((size_t)hidden * sizeof(TA)) % 16 == 0 && ((size_t)hidden * sizeof(TB)) % 16 == 0 && ((size_t)hidden * y_size) % 16 == 0) {
+    const int threads8 = (hidden / 8 + 31) / 32 * 32;
+#define LAUNCH8(TO)                                                                                               \
+    return launch_dependent(scaled_add_norm_rows_kernel<TA, TB, TO>, dim3(n_rows), dim3(threads8), 0, stream, x,  \
+                            (const TA*)a, a_partials, (size_t)a_stride, va, (const TB*)b, b_partials,             \
+                            (size_t)b_stride, vb, gain, eps, (TO*)y, hidden)
+    if (y_dtype == TOKB200_BF16) LAUNCH8(__nv_bfloat16);
+    LAUNCH8(float);
+#undef LAUNCH8
+  }
   int threads = ((hidden + 3) / 4 + 31) / 32 * 32;
   threads = threads < 32 ? 32 : threads > 1024 ? 1024 : threads;
 #define LAUNCH(TO)                                                                                              \

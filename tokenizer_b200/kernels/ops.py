@@ -1316,7 +1316,7 @@ CONV_ACTIVATIONS = {None: 0, "silu": 1}
 
 
 def short_conv(x: torch.Tensor, at: int, channels: int, w: torch.Tensor, bias, state, off: int, row_req, q_start,
-               state_slot, out: torch.Tensor, activation=None, residual: bool = False) -> None:
+               state_slot, out: torch.Tensor, activation=None, residual: bool = False, shift: bool = False) -> None:
     """out[t, c] = f(sum_j w[c, j] x[t - (taps - 1) + j, at + c] + bias[c]) (+ x[t, at + c] with `residual`)
     over the rows of each request; rows before a request's first row of the step are the taps - 1 inputs kept
     in `state` (float32 [slots, n], at `off` in the request's slot, [taps - 1, channels]).  `w` float32
@@ -1331,7 +1331,7 @@ def short_conv(x: torch.Tensor, at: int, channels: int, w: torch.Tensor, bias, s
         _sliced_ptr(x), _i(_tag(x)), _i(_ld(x)), _i(at), _i(channels), _i(taps), _ptr(w), _ptr(bias),
         _ptr(state if taps > 1 else None), _ll(state.shape[1] if taps > 1 else 0), _i(off), _ptr(row_req), _ptr(q_start),
         _ptr(state_slot), _i(CONV_ACTIVATIONS[activation]), _i(int(residual)), _ptr(out), _i(_tag(out)), _i(n),
-        _stream()), "short_conv")
+        _i(int(shift)), _stream()), "short_conv")
 
 
 def short_conv_state(x: torch.Tensor, at: int, channels: int, taps: int, state: torch.Tensor, off: int, q_start,

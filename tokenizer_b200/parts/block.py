@@ -227,11 +227,16 @@ class CausalConvResidual:
         from .base import StateNeed
         return StateNeed(((self.taps - 1) * self.hidden,)) if self.taps > 1 else None
 
+    def shape_key(self, q_lens):
+        return "conv1" if max(q_lens) == 1 else "conv"
+
     def forward(self, h, ctx, state):
         out = self.runtime.empty(h.shape[0], self.hidden)
+        single = ctx.max_q_len == 1          # a step of single tokens: the kept inputs move on in the same launch
         ops.short_conv(h, 0, self.hidden, self.weight, None, state, 0, ctx.row_req, ctx.q_start, ctx.state_slot, out,
-                       residual=True)
-        ops.short_conv_state(h, 0, self.hidden, self.taps, state, 0, ctx.q_start, ctx.state_slot)
+                       residual=True, shift=single)
+        if not single:
+            ops.short_conv_state(h, 0, self.hidden, self.taps, state, 0, ctx.q_start, ctx.state_slot)
         return out
 
 

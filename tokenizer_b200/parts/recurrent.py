@@ -284,10 +284,12 @@ class Mamba2:
         n = ctx.n_tokens
         proj = self.inputs.forward(h, out_dtype=torch.float32)
         xbc = torch.empty((n, self.channels), dtype=torch.float32, device=proj.device)
+        single = ctx.max_q_len == 1          # a step of single tokens: the kept inputs move on in the same launch
         ops.short_conv(proj, self.inner, self.channels, self.conv_w, self.conv_b, cache.state, self.conv_off, ctx.row_req,
-                       ctx.q_start, ctx.state_slot, xbc, activation="silu")
-        ops.short_conv_state(proj, self.inner, self.channels, self.taps, cache.state, self.conv_off, ctx.q_start,
-                             ctx.state_slot)
+                       ctx.q_start, ctx.state_slot, xbc, activation="silu", shift=single)
+        if not single:
+            ops.short_conv_state(proj, self.inner, self.channels, self.taps, cache.state, self.conv_off, ctx.q_start,
+                                 ctx.state_slot)
         y = torch.empty((n, self.inner), dtype=torch.float32, device=proj.device)
         ops.mamba2_scan(xbc, proj, self.inner + self.channels, self.dt_bias, self.a_log, self.skip, self.heads,
                         self.groups, self.vdim, self.n, cache.state, ctx.q_start, ctx.state_slot, y)
