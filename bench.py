@@ -1200,16 +1200,19 @@ def run_vizonex(args):
            kernel_time(lambda: ops.mamba2_scan(xbc[:rows], proj[:rows], inner + channels, dt_bias, a_log, skip, heads, groups,
                                                vdim, n_state, state, spans, slots, y[:rows])),
            rows * conv_off * 8, "gdn_scan, one token")
-    # the layer's own kernels: the convolution in front of the mixer, the scaled add with the next norm
-    h16 = rnd(T, H, dtype=torch.bfloat16)
+    # the layer's own kernels: the convolution in front of the mixer (on four times the rows: bfloat16 in and out, and
+    # the rows of T alone would fit L2), the scaled add with the next norm
+    T4 = 4 * T
+    h16 = rnd(T4, H, dtype=torch.bfloat16)
     canon = rnd(H, taps)
     side = torch.zeros(4, (taps - 1) * H, device=dev)
-    read16 = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
-    spans, slots = ints(T * r // 4 for r in range(5)), ints(range(4))
-    row_req = ints(r for r in range(4) for _ in range(T // 4))
-    record(f"short_conv added to its input, {T} x {H}, {taps} taps",
-           kernel_time(lambda: ops.short_conv(h16, 0, H, canon, None, side, 0, row_req, spans, slots, read16, residual=True)),
-           T * H * 4, "silu_gate")
+    read16 = torch.empty(T4, H, dtype=torch.bfloat16, device=dev)
+    spans4, slots4 = ints(T4 * r // 4 for r in range(5)), ints(range(4))
+    row_req4 = ints(r for r in range(4) for _ in range(T4 // 4))
+    record(f"short_conv added to its input, {T4} x {H}, {taps} taps",
+           kernel_time(lambda: ops.short_conv(h16, 0, H, canon, None, side, 0, row_req4, spans4, slots4, read16, residual=True)),
+           T4 * H * 4, "silu_gate")
+    del h16, read16
     x, a16, b16 = rnd(T, H), rnd(T, H, dtype=torch.bfloat16), rnd(T, H, dtype=torch.bfloat16)
     v1, v2, g1 = torch.ones(H, device=dev), torch.ones(H, device=dev), torch.ones(H, device=dev)
     out16 = torch.empty(T, H, dtype=torch.bfloat16, device=dev)

@@ -77,10 +77,51 @@ __device__ __forceinline__ void conv_store4(__nv_bfloat16* p, float4 v) {
   *reinterpret_cast<uint2*>(p) = raw;
 }
 
-// The same convolution for 2 to 4 taps and channels in whole 4s: a thread owns four neighbouring channels over
-// `rows` consecutive rows of the step and keeps the last TAPS - 1 inputs in registers, so that every input is
-// loaded once; where a row starts a request's portion (or the thread's run) the window is filled from the
-// rows before it and the inputs kept in the request's slot.  Sums in the order of the kernel above.
+// Four channels as they lie in memory, unpacked only where they are used: a run's inputs wait in half the registers.
+template <typename T> struct ConvRaw;
+template <> struct ConvRaw<float> { typedef float4 type; };
+template <> struct ConvRaw<__nv_bfloat16> { typedef uint2 type; };
+__device__ __forceinline__ float4 conv_load_raw(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ uint2 conv_load_raw(const __nv_bfloat16* p) { return *reinterpret_cast<const uint2*>(p); }
+__device__ __forceinline__ float4 conv_unpack(float4 v) { return v; }
+__device__ __forceinline__ float4 conv_unpack(uint2 raw) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
+// The same convolution for 2 to 4 taps and channels in whole 4s: a thread owns four neighbouring channels.
+// One row of it, wherever the row lies in its request's portion: the window is filled from the rows before it
+// and, where the portion starts within TAPS - 1 rows, from the inputs kept in the request's slot.  Sums in the
+// order of the kernel above.
+template <int TAPS>
+__device__ __forceinline__ float4 conv_row4(const float (&wt)[4][TAPS], const float4 (&win)[TAPS - 1], float4 now, float4 b4,
+                                            int act, int residual) {
+  float acc[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+  for (int k = 0; k < TAPS - 1; ++k) {
+    acc[0] = fmaf(wt[0][k], win[k].x, acc[0]);
+    acc[1] = fmaf(wt[1][k], win[k].y, acc[1]);
+    acc[2] = fmaf(wt[2][k], win[k].z, acc[2]);
+    acc[3] = fmaf(wt[3][k], win[k].w, acc[3]);
+  }
+  acc[0] = fmaf(wt[0][TAPS - 1], now.x, acc[0]);
+  acc[1] = fmaf(wt[1][TAPS - 1], now.y, acc[1]);
+  acc[2] = fmaf(wt[2][TAPS - 1], now.z, acc[2]);
+  acc[3] = fmaf(wt[3][TAPS - 1], now.w, acc[3]);
+  if (act == CONV_ACT_SILU) {
+#pragma unroll
+    for (int v = 0; v < 4; ++v) acc[v] = acc[v] / (1.0f + expf(-acc[v]));
+  }
+  if (residual) { acc[0] += now.x; acc[1] += now.y; acc[2] += now.z; acc[3] += now.w; }
+  return make_float4(acc[0], acc[1], acc[2], acc[3]);
+}
+
+// A block covers ROWS consecutive rows of the step.  A run that lies inside one request's portion, at least
+// TAPS - 1 rows behind its start, takes the straight path: the run's inputs and the TAPS - 1 rows in front of it
+// are asked for at once, before anything is waited for, every input is loaded once and the window moves through
+// registers.  Every other run (a portion's first rows, a border between requests, the step's last rows, a step
+// of single tokens, which also moves the kept inputs on) goes row by row.
 template <int TAPS, int ROWS, typename TI, typename TO>
 __global__ void __launch_bounds__(128)
 short_conv_tile_kernel(const TI* __restrict__ x, int ld, int at, int channels, const float* __restrict__ w,
@@ -88,72 +129,64 @@ short_conv_tile_kernel(const TI* __restrict__ x, int ld, int at, int channels, c
                        const int* __restrict__ row_req, const int* __restrict__ q_start,
                        const int* __restrict__ state_slot, int act, int residual, TO* __restrict__ y, int shift,
                        int n_rows) {
+  typedef typename ConvRaw<TI>::type Raw;
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
   const int t0 = blockIdx.x * ROWS;
   pdl_wait();
   pdl_launch();
   if (c >= channels) return;
   float wt[4][TAPS];
+  float4 win[TAPS - 1];                               // win[k]: the input TAPS - 1 - k rows before the current one
+  if (ROWS > 1 && !shift && t0 >= TAPS - 1 && t0 + ROWS <= n_rows) {
+    Raw in[ROWS], ahead[TAPS - 1];                    // ahead[k]: row t0 - (TAPS - 1 - k), whoever it belongs to
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) in[i] = conv_load_raw(x + (size_t)(t0 + i) * ld + at + c);
+#pragma unroll
+    for (int k = 0; k < TAPS - 1; ++k) ahead[k] = conv_load_raw(x + (size_t)(t0 - (TAPS - 1 - k)) * ld + at + c);
+    const int r = row_req[t0];
+    const int begin = r >= 0 ? q_start[r] : 0, end = r >= 0 ? q_start[r + 1] : 0;
+    if (r >= 0 && begin + TAPS - 1 <= t0 && t0 + ROWS <= end) {
+#pragma unroll
+      for (int v = 0; v < 4; ++v)
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) wt[v][j] = w[(size_t)(c + v) * TAPS + j];
+      const float4 b4 = bias ? *reinterpret_cast<const float4*>(bias + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int k = 0; k < TAPS - 1; ++k) win[k] = conv_unpack(ahead[k]);
+#pragma unroll
+      for (int i = 0; i < ROWS; ++i) {
+        const float4 now = conv_unpack(in[i]);
+        conv_store4(y + (size_t)(t0 + i) * channels + c, conv_row4<TAPS>(wt, win, now, b4, act, residual));
+#pragma unroll
+        for (int k = 0; k + 2 < TAPS; ++k) win[k] = win[k + 1];
+        win[TAPS - 2] = now;
+      }
+      return;
+    }
+  }
 #pragma unroll
   for (int v = 0; v < 4; ++v)
 #pragma unroll
     for (int j = 0; j < TAPS; ++j) wt[v][j] = w[(size_t)(c + v) * TAPS + j];
   const float4 b4 = bias ? *reinterpret_cast<const float4*>(bias + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-  float4 win[TAPS - 1];                               // win[k]: the input TAPS - 1 - k rows before the current one
-  int before = -2;
-  // the run's own inputs are asked for at once (the rows exist whoever they belong to)
-  float4 in[ROWS];
-  int owner[ROWS], begin[ROWS];                       // and so is whose they are and where those portions start
-#pragma unroll
-  for (int i = 0; i < ROWS; ++i) {
-    in[i] = t0 + i < n_rows ? conv_load4(x + (size_t)(t0 + i) * ld + at + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-    owner[i] = t0 + i < n_rows ? row_req[t0 + i] : -1;
-  }
-#pragma unroll
-  for (int i = 0; i < ROWS; ++i) begin[i] = owner[i] >= 0 ? q_start[owner[i]] : 0;
-#pragma unroll
-  for (int i = 0; i < ROWS; ++i) {
-    const int t = t0 + i;
-    if (t >= n_rows) break;
-    const int r = owner[i];
-    if (r < 0) { before = -2; continue; }
-    const int place = t - begin[i];
-    float* kept = nullptr;
-    if (r != before || place == 0 || shift) kept = state + (size_t)state_slot[r] * stride + off;
-    if (r != before || place == 0) {
-#pragma unroll
-      for (int k = 0; k < TAPS - 1; ++k) {
-        const int back = TAPS - 1 - k;
-        win[k] = back <= place ? conv_load4(x + (size_t)(t - back) * ld + at + c)
-                               : *reinterpret_cast<const float4*>(kept + (size_t)(TAPS - 1 - (back - place)) * channels + c);
-      }
-    }
-    before = r;
-    const float4 now = in[i];
-    float acc[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll 1
+  for (int t = t0; t < t0 + ROWS && t < n_rows; ++t) {
+    const int r = row_req[t];
+    if (r < 0) continue;
+    const int place = t - q_start[r];
+    float* kept = (place < TAPS - 1 || shift) ? state + (size_t)state_slot[r] * stride + off : nullptr;
 #pragma unroll
     for (int k = 0; k < TAPS - 1; ++k) {
-      acc[0] = fmaf(wt[0][k], win[k].x, acc[0]);
-      acc[1] = fmaf(wt[1][k], win[k].y, acc[1]);
-      acc[2] = fmaf(wt[2][k], win[k].z, acc[2]);
-      acc[3] = fmaf(wt[3][k], win[k].w, acc[3]);
+      const int back = TAPS - 1 - k;
+      win[k] = back <= place ? conv_unpack(conv_load_raw(x + (size_t)(t - back) * ld + at + c))
+                             : *reinterpret_cast<const float4*>(kept + (size_t)(TAPS - 1 - (back - place)) * channels + c);
     }
-    acc[0] = fmaf(wt[0][TAPS - 1], now.x, acc[0]);
-    acc[1] = fmaf(wt[1][TAPS - 1], now.y, acc[1]);
-    acc[2] = fmaf(wt[2][TAPS - 1], now.z, acc[2]);
-    acc[3] = fmaf(wt[3][TAPS - 1], now.w, acc[3]);
-    if (act == CONV_ACT_SILU) {
-#pragma unroll
-      for (int v = 0; v < 4; ++v) acc[v] = acc[v] / (1.0f + expf(-acc[v]));
-    }
-    if (residual) { acc[0] += now.x; acc[1] += now.y; acc[2] += now.z; acc[3] += now.w; }
-    conv_store4(y + (size_t)t * channels + c, make_float4(acc[0], acc[1], acc[2], acc[3]));
-#pragma unroll
-    for (int k = 0; k + 2 < TAPS; ++k) win[k] = win[k + 1];
-    win[TAPS - 2] = now;
+    const float4 now = conv_unpack(conv_load_raw(x + (size_t)t * ld + at + c));
+    conv_store4(y + (size_t)t * channels + c, conv_row4<TAPS>(wt, win, now, b4, act, residual));
     if (shift) {                                      // the only row of its request: its kept inputs move on here
 #pragma unroll
-      for (int k = 0; k < TAPS - 1; ++k) *reinterpret_cast<float4*>(kept + (size_t)k * channels + c) = win[k];
+      for (int k = 0; k + 2 < TAPS; ++k) *reinterpret_cast<float4*>(kept + (size_t)k * channels + c) = win[k + 1];
+      *reinterpret_cast<float4*>(kept + (size_t)(TAPS - 2) * channels + c) = now;
     }
   }
 }
