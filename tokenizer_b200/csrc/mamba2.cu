@@ -69,20 +69,21 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __rest
   const int first = q_start[r], n = q_start[r + 1] - first;
   if (n <= 0) return;
   float* mine = state + (size_t)state_slot[r] * stride + ((size_t)head * P + col) * N;
-  float S[NPER];
+  float2 S[NPER / 2];                      // pairs of neighbouring rows: the arithmetic below is packed, two lanes an instruction
   // a thread's rows are neighbours in the slot: 16-byte loads where the matrix has whole runs of them
   const bool whole = N == NPER * M2_PARTS && col < P && (stride & 3) == 0 && ((uintptr_t)state & 15) == 0;
   if (whole) {
 #pragma unroll
     for (int i = 0; i < NPER / 4; ++i) {
       const float4 v = *reinterpret_cast<const float4*>(mine + part * NPER + 4 * i);
-      S[4 * i] = v.x; S[4 * i + 1] = v.y; S[4 * i + 2] = v.z; S[4 * i + 3] = v.w;
+      S[2 * i] = make_float2(v.x, v.y);
+      S[2 * i + 1] = make_float2(v.z, v.w);
     }
   } else {
 #pragma unroll
-    for (int i = 0; i < NPER; ++i) {
-      const int row = part * NPER + i;
-      S[i] = (col < P && row < N) ? mine[row] : 0.f;
+    for (int i = 0; i < NPER / 2; ++i) {
+      const int row = part * NPER + 2 * i;
+      S[i] = make_float2((col < P && row < N) ? mine[row] : 0.f, (col < P && row + 1 < N) ? mine[row + 1] : 0.f);
     }
   }
   __syncthreads();                         // the zeros are written before the first copies land
@@ -144,41 +145,70 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __rest
       stage(run + RUN, half ^ 1);
       raw = raw_step(run + RUN);
     }
-    for (int k = 0; k < here; ++k) {
+    // one token of this thread's rows: S <- dec S + (dt x) B, and the rows' share of S^T C.  Two rows an
+    // instruction (each lane an IEEE multiply or fused multiply-add of its own), two sums of pairs so that
+    // the chain is half as long.
+    auto token = [&](int k) {
       const float x = xs[half][k][threadIdx.x / M2_PARTS];
       const float dec = decs[half][k], dtx = dts[half][k] * x;
       const float4* b4 = reinterpret_cast<const float4*>(&Bs[half][k][part * PADDED]);
       const float4* c4 = reinterpret_cast<const float4*>(&Cs[half][k][part * PADDED]);
-      float acc = 0.f;
+      const float2 dec2 = make_float2(dec, dec), dtx2 = make_float2(dtx, dtx);
+      float2 even = make_float2(0.f, 0.f), odd = make_float2(0.f, 0.f);
 #pragma unroll
       for (int i = 0; i < NPER / 4; ++i) {
         const float4 b = b4[i], c = c4[i];
-        S[4 * i] = fmaf(dec, S[4 * i], dtx * b.x);
-        S[4 * i + 1] = fmaf(dec, S[4 * i + 1], dtx * b.y);
-        S[4 * i + 2] = fmaf(dec, S[4 * i + 2], dtx * b.z);
-        S[4 * i + 3] = fmaf(dec, S[4 * i + 3], dtx * b.w);
-        acc = fmaf(S[4 * i], c.x, acc);
-        acc = fmaf(S[4 * i + 1], c.y, acc);
-        acc = fmaf(S[4 * i + 2], c.z, acc);
-        acc = fmaf(S[4 * i + 3], c.w, acc);
+        S[2 * i] = __ffma2_rn(dec2, S[2 * i], __fmul2_rn(dtx2, make_float2(b.x, b.y)));
+        S[2 * i + 1] = __ffma2_rn(dec2, S[2 * i + 1], __fmul2_rn(dtx2, make_float2(b.z, b.w)));
+        even = __ffma2_rn(S[2 * i], make_float2(c.x, c.y), even);
+        odd = __ffma2_rn(S[2 * i + 1], make_float2(c.z, c.w), odd);
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      const float2 both = __fadd2_rn(even, odd);
+      return both.x + both.y;
+    };
+    int k = 0;
+    // eight tokens at a time: the eight parts of a column add their shares of all eight in 4 + 2 + 1 exchanges
+    // (a part passes on the half of the sums that the other side gathers), after which part j holds token j's
+    // sum and writes it.  The pairs are those of the single token's rounds below, so a token's sum does not
+    // depend on where in a run it falls.
+    for (; k + M2_PARTS <= here; k += M2_PARTS) {
+      float acc[M2_PARTS];
+#pragma unroll
+      for (int j = 0; j < M2_PARTS; ++j) acc[j] = token(k + j);
+#pragma unroll
+      for (int width = M2_PARTS / 2; width >= 1; width >>= 1) {
+        const bool upper = (part & width) != 0;
+#pragma unroll
+        for (int j = 0; j < width; ++j) {
+          const float send = upper ? acc[j] : acc[j + width], keep = upper ? acc[j + width] : acc[j];
+          acc[j] = keep + __shfl_xor_sync(0xffffffffu, send, width);
+        }
+      }
+      if (col < P)
+        y[(size_t)(first + run + k + part) * inner + head * P + col] =
+            fmaf(d, xs[half][k + part][threadIdx.x / M2_PARTS], acc[0]);
+    }
+    for (; k < here; ++k) {
+      float acc = token(k);
       acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      if (part == 0 && col < P) y[(size_t)(first + run + k) * inner + head * P + col] = fmaf(d, x, acc);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      if (part == 0 && col < P)
+        y[(size_t)(first + run + k) * inner + head * P + col] = fmaf(d, xs[half][k][threadIdx.x / M2_PARTS], acc);
     }
     if (more) keep_step(raw, half ^ 1);
   }
   if (whole) {
 #pragma unroll
     for (int i = 0; i < NPER / 4; ++i)
-      *reinterpret_cast<float4*>(mine + part * NPER + 4 * i) = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+      *reinterpret_cast<float4*>(mine + part * NPER + 4 * i) = make_float4(S[2 * i].x, S[2 * i].y, S[2 * i + 1].x, S[2 * i + 1].y);
     return;
   }
 #pragma unroll
-  for (int i = 0; i < NPER; ++i) {
-    const int row = part * NPER + i;
-    if (col < P && row < N) mine[row] = S[i];
+  for (int i = 0; i < NPER / 2; ++i) {
+    const int row = part * NPER + 2 * i;
+    if (col < P && row < N) mine[row] = S[i].x;
+    if (col < P && row + 1 < N) mine[row + 1] = S[i].y;
   }
 }
 
