@@ -3,9 +3,10 @@
 // Per head a matrix S (N x P, float32, a request's state) and per token t of that head:
 //     dt = softplus(raw_dt + dt_bias);  S <- exp(-exp(A_log) dt) S + dt B x^T;  y = S^T C + D x
 // with x (P lanes of the head), B and C (N lanes of the head's group) the convolved and activated
-// inputs.  The columns of S are independent (column p needs x_p only), so thread (column p, part j)
-// keeps NPER neighbouring rows of column p in registers (rows j NPER .. (j + 1) NPER - 1); the 8 parts
-// of a column add their shares of S^T C in one round of shuffles.
+// inputs.  The columns of S are independent (column p needs x_p only), so a thread keeps NPER neighbouring
+// rows (rows j NPER .. (j + 1) NPER - 1 for part j) of TWO neighbouring columns in registers and reads a
+// token's B and C once for both; the 8 parts of a column add their shares of S^T C by shuffles, eight
+// tokens in 4 + 2 + 1 exchanges.  The rows' arithmetic is packed: two rows an instruction.
 //
 //   mamba2_scan      the recurrence over every request's rows of the step, token by token.  Tokens are
 //                    staged through shared memory in runs (cp.async, the next run on its way while
@@ -19,7 +20,8 @@
 
 #define M2_PARTS 8                 // threads that share a column
 #define M2_COLS 32                 // columns a block
-#define M2_THREADS (M2_PARTS * M2_COLS)
+#define M2_OWN 2                   // neighbouring columns a thread: B and C are read once for both
+#define M2_THREADS (M2_PARTS * M2_COLS / M2_OWN)
 
 __device__ __forceinline__ float m2_softplus(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
@@ -51,7 +53,7 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __rest
   __shared__ float decs[2][RUN];
   const int head = blockIdx.y, r = blockIdx.z;
   const int col0 = blockIdx.x * M2_COLS;
-  const int part = threadIdx.x % M2_PARTS, col = col0 + threadIdx.x / M2_PARTS;
+  const int part = threadIdx.x % M2_PARTS, mine_x = (threadIdx.x / M2_PARTS) * M2_OWN, col = col0 + mine_x;
   const int group = head / (heads / groups);
   const int inner = heads * P;
   const float a = expf(a_log[head]), bias = dt_bias[head], d = skip[head];
@@ -69,22 +71,27 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __rest
   const int first = q_start[r], n = q_start[r + 1] - first;
   if (n <= 0) return;
   float* mine = state + (size_t)state_slot[r] * stride + ((size_t)head * P + col) * N;
-  float2 S[NPER / 2];                      // pairs of neighbouring rows: the arithmetic below is packed, two lanes an instruction
+  float2 S[M2_OWN][NPER / 2];              // pairs of neighbouring rows: the arithmetic below is packed, two lanes an instruction
   // a thread's rows are neighbours in the slot: 16-byte loads where the matrix has whole runs of them
-  const bool whole = N == NPER * M2_PARTS && col < P && (stride & 3) == 0 && ((uintptr_t)state & 15) == 0;
+  const bool whole = N == NPER * M2_PARTS && col + M2_OWN <= P && (stride & 3) == 0 && ((uintptr_t)state & 15) == 0;
   if (whole) {
 #pragma unroll
-    for (int i = 0; i < NPER / 4; ++i) {
-      const float4 v = *reinterpret_cast<const float4*>(mine + part * NPER + 4 * i);
-      S[2 * i] = make_float2(v.x, v.y);
-      S[2 * i + 1] = make_float2(v.z, v.w);
-    }
+    for (int o = 0; o < M2_OWN; ++o)
+#pragma unroll
+      for (int i = 0; i < NPER / 4; ++i) {
+        const float4 v = *reinterpret_cast<const float4*>(mine + (size_t)o * N + part * NPER + 4 * i);
+        S[o][2 * i] = make_float2(v.x, v.y);
+        S[o][2 * i + 1] = make_float2(v.z, v.w);
+      }
   } else {
 #pragma unroll
-    for (int i = 0; i < NPER / 2; ++i) {
-      const int row = part * NPER + 2 * i;
-      S[i] = make_float2((col < P && row < N) ? mine[row] : 0.f, (col < P && row + 1 < N) ? mine[row + 1] : 0.f);
-    }
+    for (int o = 0; o < M2_OWN; ++o)
+#pragma unroll
+      for (int i = 0; i < NPER / 2; ++i) {
+        const int row = part * NPER + 2 * i;
+        const float* from = mine + (size_t)o * N;
+        S[o][i] = make_float2((col + o < P && row < N) ? from[row] : 0.f, (col + o < P && row + 1 < N) ? from[row + 1] : 0.f);
+      }
   }
   __syncthreads();                         // the zeros are written before the first copies land
   // 16 bytes a copy where rows, lanes and channels come in whole 4s (a piece of 4 rows lies inside one part)
@@ -145,26 +152,37 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __rest
       stage(run + RUN, half ^ 1);
       raw = raw_step(run + RUN);
     }
-    // one token of this thread's rows: S <- dec S + (dt x) B, and the rows' share of S^T C.  Two rows an
-    // instruction (each lane an IEEE multiply or fused multiply-add of its own), two sums of pairs so that
-    // the chain is half as long.
-    auto token = [&](int k) {
-      const float x = xs[half][k][threadIdx.x / M2_PARTS];
-      const float dec = decs[half][k], dtx = dts[half][k] * x;
+    // one token of this thread's rows: S <- dec S + (dt x) B, and the rows' share of S^T C, for both columns
+    // from one read of B and C.  Two rows an instruction (each lane an IEEE multiply or fused multiply-add of
+    // its own), two sums of pairs a column so that the chain is half as long.
+    auto token = [&](int k, float (&sum)[M2_OWN]) {
+      const float dec = decs[half][k], dt = dts[half][k];
       const float4* b4 = reinterpret_cast<const float4*>(&Bs[half][k][part * PADDED]);
       const float4* c4 = reinterpret_cast<const float4*>(&Cs[half][k][part * PADDED]);
-      const float2 dec2 = make_float2(dec, dec), dtx2 = make_float2(dtx, dtx);
-      float2 even = make_float2(0.f, 0.f), odd = make_float2(0.f, 0.f);
+      const float2 dec2 = make_float2(dec, dec);
+      float2 dtx2[M2_OWN], even[M2_OWN], odd[M2_OWN];
+#pragma unroll
+      for (int o = 0; o < M2_OWN; ++o) {
+        const float dtx = dt * xs[half][k][mine_x + o];
+        dtx2[o] = make_float2(dtx, dtx);
+        even[o] = odd[o] = make_float2(0.f, 0.f);
+      }
 #pragma unroll
       for (int i = 0; i < NPER / 4; ++i) {
         const float4 b = b4[i], c = c4[i];
-        S[2 * i] = __ffma2_rn(dec2, S[2 * i], __fmul2_rn(dtx2, make_float2(b.x, b.y)));
-        S[2 * i + 1] = __ffma2_rn(dec2, S[2 * i + 1], __fmul2_rn(dtx2, make_float2(b.z, b.w)));
-        even = __ffma2_rn(S[2 * i], make_float2(c.x, c.y), even);
-        odd = __ffma2_rn(S[2 * i + 1], make_float2(c.z, c.w), odd);
+#pragma unroll
+        for (int o = 0; o < M2_OWN; ++o) {
+          S[o][2 * i] = __ffma2_rn(dec2, S[o][2 * i], __fmul2_rn(dtx2[o], make_float2(b.x, b.y)));
+          S[o][2 * i + 1] = __ffma2_rn(dec2, S[o][2 * i + 1], __fmul2_rn(dtx2[o], make_float2(b.z, b.w)));
+          even[o] = __ffma2_rn(S[o][2 * i], make_float2(c.x, c.y), even[o]);
+          odd[o] = __ffma2_rn(S[o][2 * i + 1], make_float2(c.z, c.w), odd[o]);
+        }
       }
-      const float2 both = __fadd2_rn(even, odd);
-      return both.x + both.y;
+#pragma unroll
+      for (int o = 0; o < M2_OWN; ++o) {
+        const float2 both = __fadd2_rn(even[o], odd[o]);
+        sum[o] = both.x + both.y;
+      }
     };
     int k = 0;
     // eight tokens at a time: the eight parts of a column add their shares of all eight in 4 + 2 + 1 exchanges
@@ -172,44 +190,57 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __rest
     // sum and writes it.  The pairs are those of the single token's rounds below, so a token's sum does not
     // depend on where in a run it falls.
     for (; k + M2_PARTS <= here; k += M2_PARTS) {
-      float acc[M2_PARTS];
+      float acc[M2_PARTS][M2_OWN];
 #pragma unroll
-      for (int j = 0; j < M2_PARTS; ++j) acc[j] = token(k + j);
+      for (int j = 0; j < M2_PARTS; ++j) token(k + j, acc[j]);
 #pragma unroll
       for (int width = M2_PARTS / 2; width >= 1; width >>= 1) {
         const bool upper = (part & width) != 0;
 #pragma unroll
-        for (int j = 0; j < width; ++j) {
-          const float send = upper ? acc[j] : acc[j + width], keep = upper ? acc[j + width] : acc[j];
-          acc[j] = keep + __shfl_xor_sync(0xffffffffu, send, width);
-        }
+        for (int j = 0; j < width; ++j)
+#pragma unroll
+          for (int o = 0; o < M2_OWN; ++o) {
+            const float send = upper ? acc[j][o] : acc[j + width][o], keep = upper ? acc[j + width][o] : acc[j][o];
+            acc[j][o] = keep + __shfl_xor_sync(0xffffffffu, send, width);
+          }
       }
-      if (col < P)
-        y[(size_t)(first + run + k + part) * inner + head * P + col] =
-            fmaf(d, xs[half][k + part][threadIdx.x / M2_PARTS], acc[0]);
+#pragma unroll
+      for (int o = 0; o < M2_OWN; ++o)
+        if (col + o < P)
+          y[(size_t)(first + run + k + part) * inner + head * P + col + o] = fmaf(d, xs[half][k + part][mine_x + o], acc[0][o]);
     }
     for (; k < here; ++k) {
-      float acc = token(k);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      if (part == 0 && col < P)
-        y[(size_t)(first + run + k) * inner + head * P + col] = fmaf(d, xs[half][k][threadIdx.x / M2_PARTS], acc);
+      float acc[M2_OWN];
+      token(k, acc);
+#pragma unroll
+      for (int o = 0; o < M2_OWN; ++o) {
+        acc[o] += __shfl_xor_sync(0xffffffffu, acc[o], 4);
+        acc[o] += __shfl_xor_sync(0xffffffffu, acc[o], 2);
+        acc[o] += __shfl_xor_sync(0xffffffffu, acc[o], 1);
+        if (part == 0 && col + o < P)
+          y[(size_t)(first + run + k) * inner + head * P + col + o] = fmaf(d, xs[half][k][mine_x + o], acc[o]);
+      }
     }
     if (more) keep_step(raw, half ^ 1);
   }
   if (whole) {
 #pragma unroll
-    for (int i = 0; i < NPER / 4; ++i)
-      *reinterpret_cast<float4*>(mine + part * NPER + 4 * i) = make_float4(S[2 * i].x, S[2 * i].y, S[2 * i + 1].x, S[2 * i + 1].y);
+    for (int o = 0; o < M2_OWN; ++o)
+#pragma unroll
+      for (int i = 0; i < NPER / 4; ++i)
+        *reinterpret_cast<float4*>(mine + (size_t)o * N + part * NPER + 4 * i) =
+            make_float4(S[o][2 * i].x, S[o][2 * i].y, S[o][2 * i + 1].x, S[o][2 * i + 1].y);
     return;
   }
 #pragma unroll
-  for (int i = 0; i < NPER / 2; ++i) {
-    const int row = part * NPER + 2 * i;
-    if (col < P && row < N) mine[row] = S[i].x;
-    if (col < P && row + 1 < N) mine[row + 1] = S[i].y;
-  }
+  for (int o = 0; o < M2_OWN; ++o)
+#pragma unroll
+    for (int i = 0; i < NPER / 2; ++i) {
+      const int row = part * NPER + 2 * i;
+      float* to = mine + (size_t)o * N;
+      if (col + o < P && row < N) to[row] = S[o][i].x;
+      if (col + o < P && row + 1 < N) to[row + 1] = S[o][i].y;
+    }
 }
 
 TOKB200_API int tokb200_mamba2_scan(const float* xbc, int channels, const void* proj, int proj_dtype, int ld, int dt_at,
