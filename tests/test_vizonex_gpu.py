@@ -356,9 +356,10 @@ def test_a_far_key_among_hundreds_is_found(kernel, dtype, row):
 
 # ---- the selective state-space recurrence ---------------------------------------------------------------
 def scan_in_steps(o, xbc, proj, dt_at, dt_bias, a_log, skip, heads, groups, vdim, n_state, lengths, slots, sizes, n_slots=4,
-                  state=None):
+                  state=None, segments=None):
     """`mamba2_scan` over requests laid end to end in `xbc` / `proj`, fed in portions of `sizes` in turn; every
-    request's matrices live in its slot.  Returns y laid out like xbc, and the state arena."""
+    request's matrices live in its slot.  `segments`: into how many segments that run side by side a request's
+    rows of a step are cut (None: the kernel's own choice).  Returns y laid out like xbc, and the state arena."""
     firsts = [sum(lengths[:r]) for r in range(len(lengths))]
     if state is None:
         state = torch.full((n_slots, heads * vdim * n_state + 5), 3.0, device=DEV)      # stale numbers
@@ -373,7 +374,7 @@ def scan_in_steps(o, xbc, proj, dt_at, dt_bias, a_log, skip, heads, groups, vdim
         _, q_start = batch_of([take[r] for r in live])
         out = torch.full((rows.shape[0], heads * vdim), float("nan"), device=DEV)
         o.mamba2_scan(xbc[rows].contiguous(), proj[rows].contiguous(), dt_at, dt_bias, a_log, skip, heads, groups, vdim,
-                      n_state, state, q_start, ints([slots[r] for r in live]), out)
+                      n_state, state, q_start, ints([slots[r] for r in live]), out, segments=segments)
         y[rows] = out
         for r in live:
             done[r] += take[r]
@@ -381,12 +382,16 @@ def scan_in_steps(o, xbc, proj, dt_at, dt_bias, a_log, skip, heads, groups, vdim
     return y, state
 
 
+@pytest.mark.parametrize("segments", [None, 1, 3, 16])
 @pytest.mark.parametrize("proj_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,groups,vdim,n_state", [(8, 2, 32, 32), (3, 3, 10, 6), (2, 1, 5, 40), (2, 2, 40, 256),
                                                        (4, 1, 64, 128), (1, 1, 1, 1)])
-def test_state_space_recurrence_in_portions_and_batches_against_the_plain_one(heads, groups, vdim, n_state, proj_dtype):
+def test_state_space_recurrence_in_portions_and_batches_against_the_plain_one(heads, groups, vdim, n_state, proj_dtype,
+                                                                              segments):
     """Three requests of unlike lengths, whole in one step and then in portions down to one token on other slots:
-    both must give what the plain recurrence gives from a zero state."""
+    both must give what the plain recurrence gives from a zero state, also where a request's rows of a step run
+    as segments side by side (segments of 16 and 48 rows, requests with fewer segments than asked for, portions
+    that continue from matrices that are not zero)."""
     o = ops()
     lengths = [45, 3, 130]
     total, inner = sum(lengths), heads * vdim
@@ -408,19 +413,20 @@ def test_state_space_recurrence_in_portions_and_batches_against_the_plain_one(he
                 x64[rows, h * vdim:(h + 1) * vdim], B, C, dt[:, h], torch.exp(a_log.double().cpu()[h]), skip.double().cpu()[h])
         at += n
     args = (o, xbc, proj, dt_at, dt_bias, a_log, skip, heads, groups, vdim, n_state, lengths)
-    whole, state_a = scan_in_steps(*args, [2, 0, 3], [1000])
+    whole, state_a = scan_in_steps(*args, [2, 0, 3], [1000], segments=segments)
     close(whole, want, torch.float32, "whole", tol=5e-5)
-    pieces, state_b = scan_in_steps(*args, [1, 3, 0], [1, 2, 17, 1, 1, 40, 5])
+    pieces, state_b = scan_in_steps(*args, [1, 3, 0], [1, 2, 17, 1, 1, 40, 5], segments=segments)
     close(pieces, want, torch.float32, "in portions", tol=5e-5)
     size = heads * vdim * n_state
     close(state_b[1, :size], state_a[2, :size], torch.float32, "the matrices after the last token", tol=5e-5)
     assert float(state_a[1].min()) == 3.0 and float(state_a[2, size:].abs().max()) == 0.0      # nothing else is touched
 
 
-def test_what_a_token_wrote_far_back_is_still_in_the_state():
+@pytest.mark.parametrize("segments", [1, 4, 7])
+def test_what_a_token_wrote_far_back_is_still_in_the_state(segments):
     """Almost no decay and B, C at right angles from token to token: what token 2 wrote along its own direction
-    comes back when token 700 asks along it, across steps of 1, 2, 300 and more tokens; a state lost at a step's
-    edge gives zeros, and a slot used again starts from zero."""
+    comes back when token 700 asks along it, across steps of 1, 2, 300 and more tokens and across the segments
+    of a step; a state lost at a step's or a segment's edge gives zeros, and a slot used again starts from zero."""
     o = ops()
     heads, groups, vdim, n_state, total = 2, 1, 8, 16, 701
     inner = heads * vdim
@@ -440,13 +446,13 @@ def test_what_a_token_wrote_far_back_is_still_in_the_state():
     zeros = torch.zeros(heads, device=DEV)
     a_log = torch.full((heads,), -30.0, device=DEV)                  # decay exp(-1e-13 dt) = 1
     y, state = scan_in_steps(o, xbc, proj, 0, zeros, a_log, zeros, heads, groups, vdim, n_state, [total], [1],
-                             [1, 2, 300, 1, 397])
+                             [1, 2, 300, 1, 397], segments=segments)
     dt = math.log1p(math.exp(0.5413))
     assert torch.allclose(y[700], marker * dt, rtol=1e-5)
     # the same slot for a new request: opened (zeroed), it knows nothing of the marker
     state[1].zero_()
     y2, _ = scan_in_steps(o, xbc[3:], proj[3:], 0, zeros, a_log, zeros, heads, groups, vdim, n_state, [total - 3], [1], [1000],
-                          state=state)
+                          state=state, segments=segments)
     assert float(y2[700 - 3].abs().max()) == 0.0
 
 

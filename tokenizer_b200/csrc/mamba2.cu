@@ -37,12 +37,22 @@ __device__ __forceinline__ void m2_copy16(float* dst, const float* src) {
 
 // xbc: float32 [T, channels]: x (heads * P), B (groups * N), C (groups * N).  proj: the input product
 // [T, ld] whose columns dt_at .. + heads are the raw step sizes.
-template <int NPER, typename TI>
+//
+// PASS 0 runs a request's rows from first to last.  PASS 1 and 2 together do the same with a request's rows cut
+// into up to `segments` equal segments (whole 16s of rows) that run side by side, for steps whose requests are
+// too few to fill the device: the recurrence is linear in S, so a segment's end is (product of its decays) *
+// (its start) + (its end from a zero start).  PASS 1: segment 0 runs in full from the slot's matrices; every
+// other segment but the last runs from zero without reading C or writing y and leaves its end and the product
+// of its decays in `scratch`.  PASS 2: every segment from the second on folds the ends before it into its start,
+// then runs in full; the last one writes the slot.  (A request with one segment is done in PASS 1.)
+// scratch: [requests, segments, heads, P, N] ends, then [requests, segments, heads] products.
+template <int NPER, typename TI, int PASS>
 __global__ void __launch_bounds__(M2_THREADS)
 mamba2_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __restrict__ proj, int ld, int dt_at,
                    const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ skip,
                    int heads, int groups, int P, int N, float* __restrict__ state, long long stride,
-                   const int* __restrict__ q_start, const int* __restrict__ state_slot, float* __restrict__ y) {
+                   const int* __restrict__ q_start, const int* __restrict__ state_slot, float* __restrict__ y,
+                   float* __restrict__ scratch, int segments, int n_requests) {
   constexpr int RUN = NPER >= 32 ? 8 : 16;            // tokens staged at a time
   constexpr int PADDED = NPER + 4;                    // a part's rows and four idle lanes
   constexpr int NPAD = PADDED * M2_PARTS;
@@ -51,7 +61,8 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __rest
   __shared__ __align__(16) float xs[2][RUN][M2_COLS];
   __shared__ float dts[2][RUN];
   __shared__ float decs[2][RUN];
-  const int head = blockIdx.y, r = blockIdx.z;
+  const int head = blockIdx.y, r = PASS == 0 ? blockIdx.z : blockIdx.z / segments;
+  const int seg = PASS == 0 ? 0 : blockIdx.z % segments;
   const int col0 = blockIdx.x * M2_COLS;
   const int part = threadIdx.x % M2_PARTS, mine_x = (threadIdx.x / M2_PARTS) * M2_OWN, col = col0 + mine_x;
   const int group = head / (heads / groups);
@@ -68,30 +79,98 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __rest
     for (int i = threadIdx.x; i < 2 * RUN * M2_COLS; i += M2_THREADS) (&xs[0][0][0])[i] = 0.f;
   pdl_wait();
   pdl_launch();
-  const int first = q_start[r], n = q_start[r + 1] - first;
+  int first = q_start[r], n = q_start[r + 1] - first;
   if (n <= 0) return;
   float* mine = state + (size_t)state_slot[r] * stride + ((size_t)head * P + col) * N;
   float2 S[M2_OWN][NPER / 2];              // pairs of neighbouring rows: the arithmetic below is packed, two lanes an instruction
   // a thread's rows are neighbours in the slot: 16-byte loads where the matrix has whole runs of them
-  const bool whole = N == NPER * M2_PARTS && col + M2_OWN <= P && (stride & 3) == 0 && ((uintptr_t)state & 15) == 0;
-  if (whole) {
+  const bool whole = N == NPER * M2_PARTS && col + M2_OWN <= P && (stride & 3) == 0 && ((uintptr_t)state & 15) == 0 &&
+                     (PASS == 0 || ((uintptr_t)scratch & 15) == 0);
+  auto load = [&](const float* from, float2 (&T)[M2_OWN][NPER / 2]) {
+    if (whole) {
 #pragma unroll
-    for (int o = 0; o < M2_OWN; ++o)
+      for (int o = 0; o < M2_OWN; ++o)
 #pragma unroll
-      for (int i = 0; i < NPER / 4; ++i) {
-        const float4 v = *reinterpret_cast<const float4*>(mine + (size_t)o * N + part * NPER + 4 * i);
-        S[o][2 * i] = make_float2(v.x, v.y);
-        S[o][2 * i + 1] = make_float2(v.z, v.w);
-      }
-  } else {
+        for (int i = 0; i < NPER / 4; ++i) {
+          const float4 v = *reinterpret_cast<const float4*>(from + (size_t)o * N + part * NPER + 4 * i);
+          T[o][2 * i] = make_float2(v.x, v.y);
+          T[o][2 * i + 1] = make_float2(v.z, v.w);
+        }
+    } else {
+#pragma unroll
+      for (int o = 0; o < M2_OWN; ++o)
+#pragma unroll
+        for (int i = 0; i < NPER / 2; ++i) {
+          const int row = part * NPER + 2 * i;
+          const float* f = from + (size_t)o * N;
+          T[o][i] = make_float2((col + o < P && row < N) ? f[row] : 0.f, (col + o < P && row + 1 < N) ? f[row + 1] : 0.f);
+        }
+    }
+  };
+  auto store = [&](float* to) {
+    if (whole) {
+#pragma unroll
+      for (int o = 0; o < M2_OWN; ++o)
+#pragma unroll
+        for (int i = 0; i < NPER / 4; ++i)
+          *reinterpret_cast<float4*>(to + (size_t)o * N + part * NPER + 4 * i) =
+              make_float4(S[o][2 * i].x, S[o][2 * i].y, S[o][2 * i + 1].x, S[o][2 * i + 1].y);
+      return;
+    }
 #pragma unroll
     for (int o = 0; o < M2_OWN; ++o)
 #pragma unroll
       for (int i = 0; i < NPER / 2; ++i) {
         const int row = part * NPER + 2 * i;
-        const float* from = mine + (size_t)o * N;
-        S[o][i] = make_float2((col + o < P && row < N) ? from[row] : 0.f, (col + o < P && row + 1 < N) ? from[row + 1] : 0.f);
+        float* t = to + (size_t)o * N;
+        if (col + o < P && row < N) t[row] = S[o][i].x;
+        if (col + o < P && row + 1 < N) t[row + 1] = S[o][i].y;
       }
+  };
+  bool full = true;                        // reads C and writes y
+  float* end = mine;                       // where the matrices go when the rows are done (nullptr: nowhere)
+  float* product = nullptr;                // where the product of the decays goes
+  if (PASS == 0) {
+    load(mine, S);
+  } else {
+    const int length = (((n + segments - 1) / segments) + 15) & ~15;
+    const int count = (n + length - 1) / length;
+    if (seg >= count) return;
+    const bool last = seg == count - 1;
+    const size_t matrices = (size_t)heads * P * N;
+    float* ends = scratch + (size_t)r * segments * matrices + ((size_t)head * P + col) * N;     // + seg * matrices
+    float* products = scratch + (size_t)n_requests * segments * matrices + (size_t)r * segments * heads + head;
+    first += seg * length;
+    n = n - seg * length < length ? n - seg * length : length;
+    if (PASS == 1) {
+      if (seg == 0) {
+        load(mine, S);
+        end = last ? mine : ends;
+      } else {
+        if (last) return;
+#pragma unroll
+        for (int o = 0; o < M2_OWN; ++o)
+#pragma unroll
+          for (int i = 0; i < NPER / 2; ++i) S[o][i] = make_float2(0.f, 0.f);
+        full = false;
+        end = ends + (size_t)seg * matrices;
+        if (blockIdx.x == 0 && threadIdx.x == 0) product = products + (size_t)seg * heads;
+      }
+    } else {
+      if (seg == 0) return;
+      load(ends, S);
+      for (int j = 1; j < seg; ++j) {
+        float2 local[M2_OWN][NPER / 2];
+        load(ends + (size_t)j * matrices, local);
+        const float decay = products[(size_t)j * heads];
+        const float2 decay2 = make_float2(decay, decay);
+#pragma unroll
+        for (int o = 0; o < M2_OWN; ++o)
+#pragma unroll
+          for (int i = 0; i < NPER / 2; ++i) S[o][i] = __ffma2_rn(decay2, S[o][i], local[o][i]);
+      }
+      end = last ? mine : nullptr;
+    }
   }
   __syncthreads();                         // the zeros are written before the first copies land
   // 16 bytes a copy where rows, lanes and channels come in whole 4s (a piece of 4 rows lies inside one part)
@@ -106,7 +185,7 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __rest
         const float* src = xbc + (size_t)(first + run + k) * channels + inner + group * N + row;
         const int at = (row / NPER) * PADDED + row % NPER;
         m2_copy16(&Bs[half][k][at], src);
-        m2_copy16(&Cs[half][k][at], src + (size_t)groups * N);
+        if (full) m2_copy16(&Cs[half][k][at], src + (size_t)groups * N);
       }
       const int across = cols >> 2;
       for (int i = threadIdx.x; i < here * across; i += M2_THREADS) {
@@ -119,7 +198,7 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __rest
         const float* src = xbc + (size_t)(first + run + k) * channels + inner + group * N + row;
         const int at = (row / NPER) * PADDED + row % NPER;
         m2_copy4(&Bs[half][k][at], src);
-        m2_copy4(&Cs[half][k][at], src + (size_t)groups * N);
+        if (full) m2_copy4(&Cs[half][k][at], src + (size_t)groups * N);
       }
       for (int i = threadIdx.x; i < here * cols; i += M2_THREADS) {
         const int k = i / cols, c = i - k * cols;
@@ -139,6 +218,7 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __rest
       decs[half][threadIdx.x] = expf(-a * dt);
     }
   };
+  float decayed = 1.f;                     // the product of the decays of a run from zero
   stage(0, 0);
   keep_step(raw_step(0), 0);
   int half = 0;
@@ -185,6 +265,29 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __rest
       }
     };
     int k = 0;
+    if (PASS == 1 && !full) {              // from a zero start: the matrices and the product of the decays alone
+      for (; k < here; ++k) {
+        const float dec = decs[half][k], dt = dts[half][k];
+        const float4* b4 = reinterpret_cast<const float4*>(&Bs[half][k][part * PADDED]);
+        const float2 dec2 = make_float2(dec, dec);
+        float2 dtx2[M2_OWN];
+#pragma unroll
+        for (int o = 0; o < M2_OWN; ++o) {
+          const float dtx = dt * xs[half][k][mine_x + o];
+          dtx2[o] = make_float2(dtx, dtx);
+        }
+#pragma unroll
+        for (int i = 0; i < NPER / 4; ++i) {
+          const float4 b = b4[i];
+#pragma unroll
+          for (int o = 0; o < M2_OWN; ++o) {
+            S[o][2 * i] = __ffma2_rn(dec2, S[o][2 * i], __fmul2_rn(dtx2[o], make_float2(b.x, b.y)));
+            S[o][2 * i + 1] = __ffma2_rn(dec2, S[o][2 * i + 1], __fmul2_rn(dtx2[o], make_float2(b.z, b.w)));
+          }
+        }
+        decayed *= dec;
+      }
+    }
     // eight tokens at a time: the eight parts of a column add their shares of all eight in 4 + 2 + 1 exchanges
     // (a part passes on the half of the sums that the other side gathers), after which part j holds token j's
     // sum and writes it.  The pairs are those of the single token's rounds below, so a token's sum does not
@@ -223,39 +326,33 @@ mamba2_scan_kernel(const float* __restrict__ xbc, int channels, const TI* __rest
     }
     if (more) keep_step(raw, half ^ 1);
   }
-  if (whole) {
-#pragma unroll
-    for (int o = 0; o < M2_OWN; ++o)
-#pragma unroll
-      for (int i = 0; i < NPER / 4; ++i)
-        *reinterpret_cast<float4*>(mine + (size_t)o * N + part * NPER + 4 * i) =
-            make_float4(S[o][2 * i].x, S[o][2 * i].y, S[o][2 * i + 1].x, S[o][2 * i + 1].y);
-    return;
-  }
-#pragma unroll
-  for (int o = 0; o < M2_OWN; ++o)
-#pragma unroll
-    for (int i = 0; i < NPER / 2; ++i) {
-      const int row = part * NPER + 2 * i;
-      float* to = mine + (size_t)o * N;
-      if (col + o < P && row < N) to[row] = S[o][i].x;
-      if (col + o < P && row + 1 < N) to[row + 1] = S[o][i].y;
-    }
+  if (end != nullptr) store(end);
+  if (product != nullptr) *product = decayed;
 }
 
+// `segments` > 1: a request's rows run as that many segments side by side (two launches); `scratch` then has
+// n_requests * segments * heads * (P * N + 1) floats.
 TOKB200_API int tokb200_mamba2_scan(const float* xbc, int channels, const void* proj, int proj_dtype, int ld, int dt_at,
                                     const float* dt_bias, const float* a_log, const float* skip, int heads, int groups,
                                     int P, int N, float* state, long long stride, const int* q_start,
-                                    const int* state_slot, int n_requests, float* y, cudaStream_t stream) {
+                                    const int* state_slot, int n_requests, float* y, float* scratch, int segments,
+                                    cudaStream_t stream) {
   if (n_requests <= 0) return TOKB200_OK;
   if (heads <= 0 || groups <= 0 || heads % groups || P <= 0 || N <= 0 || N > 32 * M2_PARTS || heads > 65535 ||
-      n_requests > 65535 || channels != heads * P + 2 * groups * N || (long long)heads * P * N > stride)
+      n_requests > 65535 || channels != heads * P + 2 * groups * N || (long long)heads * P * N > stride ||
+      segments < 1 || (segments > 1 && scratch == nullptr) || (long long)n_requests * segments > 65535)
     return TOKB200_BAD_SIZE;
-  const dim3 grid((P + M2_COLS - 1) / M2_COLS, heads, n_requests);
-#define LAUNCH(NPER, TI)                                                                                          \
-  return launch_dependent(mamba2_scan_kernel<NPER, TI>, grid, dim3(M2_THREADS), 0, stream, xbc, channels,          \
-                          (const TI*)proj, ld, dt_at, dt_bias, a_log, skip, heads, groups, P, N, state, stride,     \
-                          q_start, state_slot, y)
+  const dim3 grid((P + M2_COLS - 1) / M2_COLS, heads, n_requests * segments);
+#define LAUNCH_PASS(NPER, TI, PASS)                                                                               \
+  launch_dependent(mamba2_scan_kernel<NPER, TI, PASS>, grid, dim3(M2_THREADS), 0, stream, xbc, channels,           \
+                   (const TI*)proj, ld, dt_at, dt_bias, a_log, skip, heads, groups, P, N, state, stride, q_start,   \
+                   state_slot, y, scratch, segments, n_requests)
+#define LAUNCH(NPER, TI)                                              \
+  {                                                                   \
+    if (segments == 1) return LAUNCH_PASS(NPER, TI, 0);               \
+    const int status = LAUNCH_PASS(NPER, TI, 1);                      \
+    return status != TOKB200_OK ? status : LAUNCH_PASS(NPER, TI, 2);  \
+  }
 #define BY_SIZE(TI)                                   \
   if (N <= 4 * M2_PARTS) LAUNCH(4, TI);               \
   if (N <= 8 * M2_PARTS) LAUNCH(8, TI);               \
@@ -265,6 +362,7 @@ TOKB200_API int tokb200_mamba2_scan(const float* xbc, int channels, const void* 
   if (proj_dtype == TOKB200_BF16) { BY_SIZE(__nv_bfloat16); }
 #undef BY_SIZE
 #undef LAUNCH
+#undef LAUNCH_PASS
   return TOKB200_BAD_DTYPE;
 }
 

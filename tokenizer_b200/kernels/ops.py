@@ -1385,21 +1385,49 @@ def embed_positions(ids: torch.Tensor, pos: torch.Tensor, row_req: torch.Tensor,
 MAMBA2_MAX_STATE = 256
 
 
+_M2_SEGMENTS = int(os.environ.get("TOKB200_M2_SEGMENTS", "0"))     # > 0: that many segments a request, whatever the step
+MAMBA2_MAX_SEGMENTS = 16
+
+
+def mamba2_segments(n_rows: int, n_requests: int, heads: int, vdim: int) -> int:
+    """Into how many segments that run side by side `mamba2_scan` cuts a request's rows: as many as give every
+    multiprocessor a few blocks (a block is 32 columns of a head and request), none shorter than 64 rows on
+    average; 1 for steps whose requests fill the device by themselves and for decoding steps.  It depends on
+    the step's shape alone, so a captured step replays with the same launches."""
+    if _M2_SEGMENTS > 0:
+        return min(_M2_SEGMENTS, MAMBA2_MAX_SEGMENTS)
+    blocks = -(-vdim // 32) * heads * max(1, n_requests)
+    return max(1, min(592 // blocks, n_rows // (64 * max(1, n_requests)), MAMBA2_MAX_SEGMENTS))
+
+
 def mamba2_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_at: int, dt_bias, a_log, skip, heads: int, groups: int,
-                vdim: int, n_state: int, state: torch.Tensor, q_start, state_slot, y: torch.Tensor) -> None:
+                vdim: int, n_state: int, state: torch.Tensor, q_start, state_slot, y: torch.Tensor,
+                segments: Optional[int] = None) -> None:
     """Per head and token: dt = softplus(proj[dt_at + head] + dt_bias); S <- exp(-exp(a_log) dt) S + dt B x^T;
     y = S^T C + skip x, over every request's rows.  `xbc` float32 [T, heads * vdim + 2 groups * n_state] (x, B,
     C); `state` float32 [slots, n] with a slot's matrices [heads, vdim, n_state] at its start; `y` float32
-    [T, heads * vdim]."""
+    [T, heads * vdim].  `segments` > 1: every request's rows of the step are cut into that many equal segments
+    that run side by side (the recurrence is linear in S: a segment's end is the product of its decays times
+    its start plus its end from a zero start), two launches; None: `mamba2_segments` chooses."""
     n = xbc.shape[0]
     if xbc.dtype != torch.float32 or y.dtype != torch.float32 or tuple(y.shape) != (n, heads * vdim) or \
             xbc.shape[1] != heads * vdim + 2 * groups * n_state or state.dtype != torch.float32 or state.dim() != 2 or \
             dt_at + heads > proj.shape[1] or any(v.dtype != torch.float32 or v.numel() != heads for v in (dt_bias, a_log, skip)):
         raise ValueError("mamba2_scan: sizes of the inputs, the state or the output disagree")
+    n_requests = q_start.shape[0] - 1
+    if segments is None:
+        segments = mamba2_segments(n, n_requests, heads, vdim)
+    if not 1 <= segments <= MAMBA2_MAX_SEGMENTS:
+        raise ValueError(f"mamba2_scan: 1 to {MAMBA2_MAX_SEGMENTS} segments")
+    # the segments' ends (as the slot's matrices) and the products of their decays
+    scratch = torch.empty(n_requests * segments * heads * (vdim * n_state + 1), dtype=torch.float32,
+                          device=xbc.device) if segments > 1 else None
     _check(_lib("mamba2").tokb200_mamba2_scan(
         _ptr(xbc), _i(xbc.shape[1]), _sliced_ptr(proj), _i(_tag(proj)), _i(_ld(proj)), _i(dt_at), _ptr(dt_bias), _ptr(a_log),
         _ptr(skip), _i(heads), _i(groups), _i(vdim), _i(n_state), _ptr(state), _ll(state.shape[1]), _ptr(q_start),
-        _ptr(state_slot), _i(q_start.shape[0] - 1), _ptr(y), _stream()), "mamba2_scan")
+        _ptr(state_slot), _i(n_requests), _ptr(y), _ptr(scratch), _i(segments), _stream()), "mamba2_scan")
+    if segments > 1:
+        counter.launches += 1
 
 
 def mamba2_out_norm(y: torch.Tensor, proj: torch.Tensor, z_at: int, gain: torch.Tensor, eps: float, parts: int,
