@@ -671,6 +671,32 @@ def test_mixed_batches_on_pages_and_slots_that_are_used_again(model, dtype, live
     compare(got, want, dtype, "mixed")
 
 
+@pytest.mark.parametrize("kind", ["state_space", "attention"])
+def test_models_of_one_kind_of_mixer_alone(kind, tmp_path_factory):
+    """Layers of one kind only: a model that keeps no keys at all (every layer the recurrence: no page is ever
+    read) and one that keeps no matrices, whole and in mixed batches on slots that are used again, float32."""
+    from tiny_vizonex import attention, config, dense, mamba2, moe
+    from tokenizer_b200 import write_random_model
+    if kind == "state_space":
+        cfg = config([mamba2(6, 12, 24, 3, 3, 2, dense(44)), mamba2(2, 36, 48, 1, 2, 4),
+                      mamba2(4, 20, 8, 2, 4, 1, moe(5, 2, 12, 1.2, 1.7, shared=(20, 0.9)))],
+                     vocab=210, width=72, eps=4e-6, taps=2)
+    else:
+        cfg = config([attention(5, 5, 12, 12, 0.7, size=33, mlp=dense(52)), attention(4, 1, 20, 28, 0.5, size=9),
+                      attention(3, 1, 24, 8, 0.45, mlp=moe(6, 4, 10, 0.9, 1.3, groups=(2, 2)))],
+                     vocab=190, width=60, eps=1e-5, taps=3)
+    folder, page = str(tmp_path_factory.mktemp(f"vizonex_{kind}")), 16
+    write_random_model(folder, cfg, 11, scale=SHARPEN)
+    requests = {f"r{i}": random_ids(n, cfg.vocab, 500 + i) for i, n in enumerate([2, 70, 35, 141, 18, 66])}
+    want = reference_logits(folder, requests)
+    steps = ru.steps_whole(requests)
+    got = ru.collect(steps, replay(folder, "float32", steps, max(ru.rounded64(len(v)) for v in requests.values()), page))
+    ru.compare(got, want, "float32", f"{kind} alone, whole")
+    steps, peak = ru.steps_mixed(requests, max_live=3, seed=5)
+    got = ru.collect(steps, replay(folder, "float32", steps, peak, page, max_requests=3))
+    ru.compare(got, want, "float32", f"{kind} alone, mixed")
+
+
 def test_experts_chosen_token_by_token(tmp_path_factory):
     """With the router left as drawn, which experts a token uses changes from token to token (the other
     whole-model runs pin the choice, see `settle_routing`); in float32 a near tie is out of reach of rounding."""
