@@ -1,0 +1,620 @@
+"""The Zobelorn decoder on the GPU against the plain restatement: each mechanism's kernels alone, with
+weights or inputs made so that a fault shows (a key just outside a window, a score far above the cap, a far
+key among hundreds), then whole models (four tiny configurations of unlike sizes) whole, token by token, in
+portions, in mixed batches on few pages and slots, and through the generation entry point."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_zobelorn as plain
+import replay_util as ru
+from tiny import random_ids
+from tiny_zobelorn import SHARPEN, TINY, make_folder, reference_logits
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ops():
+    from tokenizer_b200.kernels import ops as o
+    return o
+
+
+def rnd(*shape, seed=0, dtype=torch.float32, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def close(got, want, dtype, what="", tol=None):
+    got, want = got.detach().float().cpu(), want.detach().float().cpu()
+    tol = tol if tol is not None else (2e-5 if dtype == torch.float32 else 2e-2)
+    bound = tol * max(1.0, float(want.abs().max()))
+    err = float((got - want).abs().max())
+    assert torch.isfinite(got).all() and err <= bound, f"{what}: max |diff| {err:.3e} > {bound:.3e}"
+
+
+def ints(values):
+    return torch.tensor(list(values), dtype=torch.int32, device=DEV)
+
+
+# ---- the norm behind a sublayer, the add and the next norm ----------------------------------------------
+@pytest.mark.parametrize("width", [50, 320, 2048, 8192, 9001])
+@pytest.mark.parametrize("form", ["bf16", "f32", "partials"])
+@pytest.mark.parametrize("then", [True, False])
+def test_a_normed_output_is_added_and_the_sum_is_normed(width, form, then):
+    """x += post(y) with gains 1 + w and a multiplier folded in, then the next norm of the new x, one launch."""
+    o = ops()
+    n, eps, mult = 5, 1e-5, 0.3
+    x = rnd(n, width, seed=1, scale=3.0)
+    w_post, w_next = rnd(width, seed=2, scale=0.2), rnd(width, seed=3, scale=0.2)
+    if form == "bf16":
+        y = rnd(n, width, seed=4, dtype=torch.bfloat16, scale=7.0)
+        total = y.double()
+    elif form == "f32":
+        y = rnd(n, width, seed=4, scale=7.0)
+        total = y.double()
+    else:
+        y = rnd(3, n, width, seed=4, scale=7.0)
+        total = y.double().sum(0)
+    gain_post = ((w_post + 1.0) * mult).contiguous()
+    gain_next = (w_next + 1.0).contiguous()
+    want_x = x.double().cpu() + mult * plain.layer_norm_one_plus(total.cpu(), w_post.double().cpu(), eps)
+    got_x = x.clone()
+    out = torch.full((n, width), float("nan"), device=DEV) if then else None
+    o.post_norm_add(got_x, [(y, 1.0)], gain_post, None, eps, gain_next if then else None, None, 2e-6, out, rms=True,
+                    next_rms=True)
+    close(got_x, want_x, torch.float32, "the stream")
+    if then:
+        close(out, plain.layer_norm_one_plus(want_x, w_next.double().cpu(), 2e-6), torch.float32, "the next norm")
+
+
+def test_norm_parts_of_a_layer_fold_one_plus_and_the_multiplier():
+    """The registered norm with `one_plus` and `gain_scale`, as a block uses it: `add_to` with and without a norm
+    that follows, and `forward` with a row gather."""
+    from tokenizer_b200.config.spec import PartSpec
+    from tokenizer_b200.parts.base import Runtime, build_part
+    from tokenizer_b200.weights.store import WeightStore
+    width, eps = 72, 1e-6
+    w1, w2 = rnd(width, seed=5, scale=0.3).cpu().bfloat16(), rnd(width, seed=6, scale=0.3).cpu().bfloat16()
+    store = WeightStore({"a": w1, "b": w2})
+    rt = Runtime(torch.device(DEV), torch.float32)
+    post = build_part("norm", PartSpec("rms_norm", {"size": width, "eps": eps, "tensor": "a", "one_plus": True,
+                                                    "gain_scale": 0.25}, "a"), store, rt)
+    front = build_part("norm", PartSpec("rms_norm", {"size": width, "eps": eps, "tensor": "b", "one_plus": True}, "b"), store, rt)
+    x, y = rnd(4, width, seed=7), rnd(4, width, seed=8, scale=5.0)
+    want_x = x.double().cpu() + 0.25 * plain.layer_norm_one_plus(y.double().cpu(), w1.double(), eps)
+    got_x = x.clone()
+    h = post.add_to(got_x, [(y, 1.0)], then=front)
+    close(got_x, want_x, torch.float32, "add_to")
+    close(h, plain.layer_norm_one_plus(want_x, w2.double(), eps), torch.float32, "the norm that follows")
+    again = x.clone()
+    assert post.add_to(again, [(y, 1.0)]) is None
+    close(again, want_x, torch.float32, "add_to alone")
+    rows = ints([3, 1])
+    close(front.forward(got_x, rows=rows), plain.layer_norm_one_plus(want_x[[3, 1]], w2.double(), eps), torch.float32, "gathered")
+
+
+# ---- queries, keys and values: norms, the two layouts of the rotation, queries alone ----------------------
+def rotate_store(proj, pos, heads, kv, dim, vdim, row, dtype, freqs, layout, q_gain=None, k_gain=None, eps=0.0,
+                 head_norm=None, own=True):
+    o = ops()
+    n = proj.shape[0]
+    q = torch.full((n, heads * row), float("nan"), dtype=dtype, device=DEV)
+    pools = [torch.full((n + 3, kv, row), float("nan"), dtype=dtype, device=DEV) for _ in range(2)] if own else [None, None]
+    slots = ints(range(n, 0, -1)) if own else None          # rows written back to front, slot 0 left alone
+    inv = torch.tensor(freqs, dtype=torch.float64).to(torch.float32).to(DEV) if freqs else None
+    o.qkv_rotate_store(proj, 2, None, inv, 2 * len(freqs), ints(pos), slots, ints([0] * n), q, pools[0], pools[1], heads,
+                       kv if own else 0, dim, vdim, row, q_gain=q_gain, k_gain=k_gain, eps=eps, layout=layout,
+                       head_norm_eps=head_norm)
+    return q, pools
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv,dim,vdim,rot", [(6, 2, 64, 128, 64), (3, 3, 10, 20, 4), (4, 1, 32, 16, 16), (1, 1, 24, 24, 0)])
+def test_whole_projection_norms_then_the_half_layout_on_leading_lanes(heads, kv, dim, vdim, rot, dtype):
+    n, eps, factor = 7, 1e-5, 8.0
+    row = -(-max(dim, vdim) // 16) * 16
+    proj = rnd(n, 2 + heads * dim + kv * (dim + vdim) + 5, seed=11, scale=2.0)
+    q_gain, k_gain = rnd(heads * dim, seed=12) + 1.0, rnd(kv * dim, seed=13) + 1.0
+    pos = [0, 1, 2, 900, 901, 77, 5000]
+    freqs = plain.linear_frequencies(10000.0, rot, factor) if rot else []
+    q, pools = rotate_store(proj, pos, heads, kv, dim, vdim, row, dtype, freqs, "half", q_gain, k_gain, eps)
+    p = proj.double().cpu()[:, 2:]
+    positions = torch.tensor(pos)
+    want_q = plain.root_mean_square_norm(p[:, :heads * dim], eps, q_gain.double().cpu()).view(n, heads, dim)
+    want_k = plain.root_mean_square_norm(p[:, heads * dim:(heads + kv) * dim], eps, k_gain.double().cpu()).view(n, kv, dim)
+    want_q, want_k = plain.rotate(want_q, positions, freqs, "half"), plain.rotate(want_k, positions, freqs, "half")
+    want_v = p[:, (heads + kv) * dim:(heads + kv) * dim + kv * vdim].view(n, kv, vdim)
+    tol = 3e-4 if dtype == torch.float32 else 2e-2       # the 32-bit angle at position 5,000 is good to about 3e-4
+    close(q.view(n, heads, row)[:, :, :dim], want_q, dtype, "queries", tol)
+    back = list(range(n, 0, -1))
+    close(pools[0][back][:, :, :dim], want_k, dtype, "keys", tol)
+    close(pools[1][back][:, :, :vdim], want_v, dtype, "values", tol)
+    assert float(q.view(n, heads, row)[:, :, dim:].float().abs().max() if row > dim else 0.0) == 0.0     # zeros behind
+    assert torch.isnan(pools[0][0].float()).all()         # a slot of no token is left alone
+    if rot and rot < dim:                                  # lanes behind the rotated ones pass unchanged
+        flat = plain.root_mean_square_norm(p[:, :heads * dim], eps, q_gain.double().cpu()).view(n, heads, dim)
+        close(q.view(n, heads, row)[:, :, rot:dim], flat[:, :, rot:], dtype, "unrotated lanes", tol)
+    if rot:                                                # the interleaved pairing would give other numbers
+        other = plain.rotate(plain.root_mean_square_norm(p[:, :heads * dim], eps, q_gain.double().cpu()).view(n, heads, dim),
+                             positions, freqs, "interleaved")
+        assert float((other - want_q).abs().max()) > 0.1
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv,dim,vdim,rot", [(4, 2, 64, 64, 64), (2, 1, 6, 10, 2), (5, 5, 48, 16, 16), (33, 3, 16, 16, 0)])
+def test_interleaved_rotation_then_a_norm_a_head_without_gain(heads, kv, dim, vdim, rot, dtype):
+    n, eps = 6, 1e-6
+    row = -(-max(dim, vdim) // 16) * 16
+    proj = rnd(n, 2 + heads * dim + kv * (dim + vdim), seed=15, scale=3.0)
+    proj[:, 2:2 + dim] *= 20.0                            # head 0 far larger than the others: a norm over the whole
+    pos = [0, 3, 64, 65, 1000, 31]                        # projection would leave it so, a norm a head does not
+    freqs = plain.banded_frequencies(500.0, rot, 8.0, 1.0, 4.0, 64) if rot else []
+    q, pools = rotate_store(proj, pos, heads, kv, dim, vdim, row, dtype, freqs, "interleaved", head_norm=eps)
+    p, positions = proj.double().cpu()[:, 2:], torch.tensor(pos)
+    want_q = plain.root_mean_square_norm(plain.rotate(p[:, :heads * dim].view(n, heads, dim), positions, freqs, "interleaved"), eps)
+    want_k = plain.root_mean_square_norm(
+        plain.rotate(p[:, heads * dim:(heads + kv) * dim].view(n, kv, dim), positions, freqs, "interleaved"), eps)
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    close(q.view(n, heads, row)[:, :, :dim], want_q, dtype, "queries", tol)
+    back = list(range(n, 0, -1))
+    close(pools[0][back][:, :, :dim], want_k, dtype, "keys", tol)
+    got_sizes = q.view(n, heads, row).float().pow(2).sum(-1).cpu()
+    assert float((got_sizes / dim - 1.0).abs().max()) < 0.05          # every head has mean square one
+    # queries alone, for a layer that reads another layer's cache: the same queries, nothing else written
+    alone = torch.cat([proj[:, :2 + heads * dim], proj[:, :3]], dim=1).contiguous()
+    q2, _ = rotate_store(alone, pos, heads, kv, dim, vdim, row, dtype, freqs, "interleaved", head_norm=eps, own=False)
+    assert torch.equal(q2, q)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,vdim,row", [(3, 20, 32), (4, 64, 64), (1, 5, 16)])
+def test_sigmoid_gate_on_the_heads_outputs(heads, vdim, row, dtype):
+    o = ops()
+    n = 9
+    mixed = rnd(n, heads * row, seed=21, dtype=dtype)
+    proj = rnd(n, 7 + heads * vdim, seed=22, scale=3.0)
+    want = mixed.double().cpu().view(n, heads, row).clone()
+    want[:, :, :vdim] *= plain.sigmoid(proj.double().cpu()[:, 7:].view(n, heads, vdim))
+    o.attention_gate(mixed, proj, 7, heads, vdim, row)
+    close(mixed.view(n, heads, row), want, dtype, "gated", 1e-6 if dtype == torch.float32 else 1e-2)
+
+
+# ---- windows, chunks and the cap in every attention kernel ------------------------------------------------
+def paged(lengths, kv, row, page, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    n_pages = sum(-(-n // page) for n in lengths) + 2
+    order = torch.randperm(n_pages, generator=g).tolist()
+    pools = [torch.full((n_pages * page, kv, row), float("nan"), dtype=dtype) for _ in range(2)]
+    tables = torch.full((len(lengths), max(-(-n // page) for n in lengths) + 1), -1, dtype=torch.int32)
+    dense = [[torch.randn(n, kv, row, generator=g).to(dtype), torch.randn(n, kv, row, generator=g).to(dtype)] for n in lengths]
+    return pools, tables, dense, order
+
+
+def scatter(pools, tables, dense, order, page):
+    for r, (k, v) in enumerate(dense):
+        for b in range(-(-k.shape[0] // page)):
+            pg = order.pop()
+            tables[r, b] = pg
+            rows = slice(b * page, min(k.shape[0], (b + 1) * page))
+            pools[0][pg * page:pg * page + rows.stop - rows.start] = k[rows]
+            pools[1][pg * page:pg * page + rows.stop - rows.start] = v[rows]
+
+
+def run_attention(kernel, q, pools, tables, row_req, pos, spans, heads, kv, row, page, scale, window, chunk, softcap):
+    from tokenizer_b200.parts.attention import RowTiles
+    o = ops()
+    out = torch.full((len(pos), heads * row), float("nan"), dtype=q.dtype, device=DEV)
+    args = (q.to(DEV).view(len(pos), -1), pools[0].to(DEV), pools[1].to(DEV), out, tables.to(DEV), ints(row_req), ints(pos))
+    if kernel == "generic":
+        o.paged_attention_generic(*args, heads, kv, row, page, window, scale, chunk=chunk, softcap=softcap)
+    elif kernel == "decode":
+        o.decode_attention(*args, heads, kv, row, page, window, scale, chunk=chunk, softcap=softcap)
+    else:
+        note = RowTiles(o.WIDE_TILE_ROWS if kernel == "wide" else o.PREFILL_TILE_ROWS)
+        words = np.zeros(note.capacity(len(pos), len(spans)), dtype=np.int32)
+        counts = np.array([m for _, _, m in spans], dtype=np.int32)
+        firsts = np.concatenate(([0], np.cumsum(counts)[:-1])).astype(np.int32)
+        n_tiles = note.fill(words, firsts, counts, np.array([f for _, f, _ in spans], dtype=np.int32), False)
+        tiles = torch.tensor(words, device=DEV).view(-1, 2)
+        run = o.attention_tcgen05 if kernel == "wide" else o.prefill_attention
+        run(*args, tiles, n_tiles, heads, kv, row, page, window, scale, chunk=chunk, softcap=softcap)
+    return out.view(len(pos), heads, row).float().cpu()
+
+
+def plain_rows(q, dense, row_req, pos, scale, size, chunk, softcap):
+    """Every row's output from `plain.attend`, one call a request over its whole length (rows that are not in
+    the step ask with zeros and are dropped).  `size`: the window's keys; `chunk`: the chunk's positions."""
+    out = torch.zeros(q.shape, dtype=torch.float64)
+    for r, (k, v) in enumerate(dense):
+        mine = [t for t in range(q.shape[0]) if row_req[t] == r]
+        if not mine:
+            continue
+        n = k.shape[0]
+        queries = torch.zeros(n, q.shape[1], q.shape[2], dtype=torch.float64)
+        queries[[pos[t] for t in mine]] = q[mine].double()
+        visible = plain.visible_chunk(n, chunk) if chunk else plain.visible_window(n, size if size else n + 1)
+        full = plain.attend(queries, k.double(), v.double(), visible, scale, softcap).view(n, q.shape[1], -1)
+        out[mine] = full[[pos[t] for t in mine]]
+    return out
+
+
+ATTENTION_CASES = [
+    # kernel, dtype, heads, kv heads, lanes, window's keys, chunk, cap
+    ("generic", torch.float32, 3, 3, 48, 50, None, 4.0), ("generic", torch.bfloat16, 4, 2, 144, 33, None, None),
+    ("generic", torch.float32, 2, 1, 32, 1, None, 2.0), ("generic", torch.float32, 2, 1, 16, None, 37, None),
+    ("decode", torch.bfloat16, 4, 2, 32, 96, None, 30.0), ("decode", torch.bfloat16, 16, 1, 64, 37, None, 3.0),
+    ("decode", torch.bfloat16, 2, 2, 128, 300, None, None), ("decode", torch.bfloat16, 2, 2, 48, None, 64, None),
+    ("decode", torch.bfloat16, 4, 1, 64, 1, None, 5.0),
+    ("tiles", torch.bfloat16, 3, 3, 48, 37, None, 3.0), ("tiles", torch.bfloat16, 4, 2, 80, 160, None, None),
+    ("tiles", torch.bfloat16, 2, 2, 16, 1, None, 8.0), ("tiles", torch.bfloat16, 2, 1, 64, None, 64, None),
+    ("wide", torch.bfloat16, 4, 2, 128, 160, None, 30.0), ("wide", torch.bfloat16, 6, 3, 128, 37, None, 2.0),
+    ("wide", torch.bfloat16, 2, 1, 64, 96, None, None), ("wide", torch.bfloat16, 2, 1, 64, None, 100, None),
+    ("wide", torch.bfloat16, 2, 1, 64, None, None, 6.0)]
+
+
+@pytest.mark.parametrize("kernel,dtype,heads,kv,row,size,chunk,softcap", ATTENTION_CASES)
+def test_window_edges_and_the_cap_in_every_attention_kernel(kernel, dtype, heads, kv, row, size, chunk, softcap):
+    """For every request's last row, the key just outside its window (or chunk) and the oldest key inside get
+    scores that stand out and values of their own: the one must be missing from the output, the other must
+    weigh in; with a cap it weighs no more than the cap allows, however large its raw score.  Requests end right
+    behind, on and before an edge, and one of them is a single token."""
+    page, edge = 16, size or chunk or 100
+    lengths = [3 * edge + 2, 2 * edge + 1, 1, 4 * edge] if edge > 1 else [70, 33, 1, 16]
+    pools, tables, dense, order = paged(lengths, kv, row, page, dtype, seed=60)
+    scale = 1.0 / math.sqrt(row)
+    if kernel == "decode":
+        row_req, pos, spans = [0, 1, 2, 3], [n - 1 for n in lengths], None
+    else:
+        take = [min(n, 130) for n in lengths]
+        spans = [(r, n - m, m) for r, (n, m) in enumerate(zip(lengths, take))]
+        row_req = [r for r, _, m in spans for _ in range(m)]
+        pos = [first + i for _, first, m in spans for i in range(m)]
+    q = rnd(len(pos), heads, row, seed=61, dtype=dtype).cpu()
+    last = [t for t in range(len(pos)) if t + 1 == len(pos) or row_req[t + 1] != row_req[t]]
+    for t in last:
+        if chunk:
+            start = pos[t] - pos[t] % chunk
+        else:
+            start = max(0, pos[t] - size + 1) if size else 0
+        k, v = dense[row_req[t]]
+        direction = q[t, 0].float() / q[t, 0].float().norm()
+        if start > 0:
+            k[start - 1, 0] = (direction * 40.0).to(dtype)
+            v[start - 1, 0] = 50.0
+        if start < pos[t]:
+            k[start, 0] = (direction * 20.0).to(dtype)
+            v[start, 0] = -9.0
+    scatter(pools, tables, dense, order, page)
+    window = size - 1 if size else None
+    got = run_attention(kernel, q, pools, tables, row_req, pos, spans, heads, kv, row, page, scale, window, chunk, softcap)
+    want = plain_rows(q, dense, row_req, pos, scale, size, chunk, softcap)
+    assert torch.isfinite(got).all()
+    bound = 2e-5 if dtype == torch.float32 else 3e-2
+    assert float((got - want).abs().max()) <= bound * max(1.0, float(want.abs().max()))
+    if edge > 1:     # the edge matters: seeing the key just outside would pull head 0 of the planted rows to its value
+        open_ = plain_rows(q, dense, row_req, pos, scale, None, None, softcap)
+        assert float((open_ - want).abs().max()) > 1.0
+    if softcap and edge > 1:                # the cap matters: without it the planted key inside would take all the weight
+        free = plain_rows(q, dense, row_req, pos, scale, size, chunk, None)
+        assert float((free - want).abs().max()) > 0.5
+
+
+@pytest.mark.parametrize("kernel,dtype,row", [("generic", torch.float32, 48), ("decode", torch.bfloat16, 64),
+                                              ("tiles", torch.bfloat16, 48), ("wide", torch.bfloat16, 128)])
+def test_a_far_key_among_hundreds_is_found_through_the_cap(kernel, dtype, row):
+    """Without a window, key 3 of 1,500 carries the last query's own direction: although the cap bounds its score
+    at 12, far above the others', its value must come back nearly whole, from whichever page it lies on."""
+    heads, kv, page, n = 2, 1, 16, 1500
+    pools, tables, dense, order = paged([n], kv, row, page, dtype, seed=70)
+    take = 1 if kernel == "decode" else 200
+    spans = [(0, n - take, take)]
+    row_req, pos = [0] * take, list(range(n - take, n))
+    q = rnd(take, heads, row, seed=71, dtype=dtype, scale=0.3).cpu()
+    k, v = dense[0]
+    k[3, 0] = (q[-1, 1].float() / q[-1, 1].float().norm() * 400.0).to(dtype)
+    v[3, 0] = 7.0
+    scatter(pools, tables, dense, order, page)
+    scale = 1.0 / math.sqrt(row)
+    got = run_attention(kernel, q, pools, tables, row_req, pos, spans, heads, kv, row, page, scale, None, None, 12.0)
+    want = plain_rows(q, dense, row_req, pos, scale, None, None, 12.0)
+    assert float((got - want).abs().max()) <= (2e-5 if dtype == torch.float32 else 3e-2) * 7.0
+    assert float((got[-1, 1] - 7.0).abs().max()) < 0.5
+
+
+# ---- experts whose weight multiplies their input ------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("experts,top,ff,shared", [(6, 2, 40, 56), (4, 1, 64, 0), (3, 3, 14, 10), (12, 5, 8, 0)])
+def test_sigmoid_scores_choose_and_multiply_the_experts_input(experts, top, ff, shared, dtype):
+    o = ops()
+    n, hidden = 11, 48
+    h = rnd(n, hidden, seed=31, dtype=dtype)
+    router = rnd(experts, hidden, seed=32, scale=0.5)
+    share = torch.full((n, experts + (1 if shared else 0)), float("nan"), device=DEV)
+    o.moe_route(h, router, experts, top, "one" if shared else None, share, score="sigmoid")
+    scores = plain.sigmoid(h.double().cpu() @ router.double().cpu().t())
+    want_share = torch.zeros(n, experts, dtype=torch.float64)
+    for t in range(n):
+        for e in sorted(range(experts), key=lambda e: (-float(scores[t, e]), e))[:top]:
+            want_share[t, e] = scores[t, e]
+    close(share[:, :experts], want_share, torch.float32, "weights: the chosen experts' scores, not renormalised", 1e-5)
+    if shared:
+        assert float((share[:, experts] - 1.0).abs().max()) == 0.0
+    inner = experts * ff + shared
+    gu = rnd(n, 2 * inner, seed=33, dtype=dtype, scale=2.0)
+    act = torch.full((n, inner), float("nan"), dtype=dtype, device=DEV)
+    o.moe_gate(gu, share, act, experts, ff, bool(shared), "silu", on_input=True)
+    g, u = gu.double().cpu()[:, :inner], gu.double().cpu()[:, inner:]
+    lane_share = torch.cat([share[:, :experts].double().cpu().repeat_interleave(ff, dim=1),
+                            torch.ones(n, shared, dtype=torch.float64)], dim=1)
+    want = plain.silu(lane_share * g) * (lane_share * u)
+    close(act, want, dtype, "lanes", 1e-5 if dtype == torch.float32 else 1e-2)
+    on_output = plain.silu(g) * u * lane_share
+    assert float((on_output - want).abs().max()) > 0.1
+
+
+# ---- whole models -----------------------------------------------------------------------------------
+LENGTHS = {"a": [1, 2, 23, 100, 131, 49], "b": [5, 19, 97, 201, 260, 100], "c": [3, 40, 130, 64, 1, 90],
+           "d": [4, 31, 77, 150, 9, 60]}
+
+
+@pytest.fixture(scope="module", params=sorted(TINY))
+def model(request, tmp_path_factory):
+    folder, cfg, page = make_folder(tmp_path_factory, request.param)
+    requests = {f"r{i}": random_ids(n, cfg.vocab, 300 + i) for i, n in enumerate(LENGTHS[request.param])}
+    return folder, cfg, page, requests, reference_logits(folder, requests)
+
+
+def replay(folder, dtype, steps, max_tokens, page, max_requests=4, use_graphs=True):
+    """What the replay program does, inside this process: every step through `Engine.step` on a pool of
+    `max_tokens` tokens and `max_requests` slots; returns {step: logits}."""
+    from tokenizer_b200.engine import Engine, StepEntry
+    engine = Engine.from_folder(folder, dtype=dtype, num_pages=-(-max_tokens // page), page_size=page,
+                                max_requests=max_requests, use_graphs=use_graphs)
+    live, out = {}, {}
+    for record in steps:
+        entries = []
+        for item in record["entries"]:
+            if item["id"] not in live:
+                live[item["id"]] = engine.cache.open(item["id"])
+            engine.cache.reserve(live[item["id"]], len(item["tokens"]))
+            entries.append(StepEntry(live[item["id"]], item["tokens"], item.get("want", [])))
+        logits = engine.step(entries)
+        if logits.shape[0]:
+            out[record["step"]] = logits.cpu().numpy()
+        for name in record.get("end", []):
+            engine.cache.close(live.pop(name))
+        engine.cache.check()
+    engine.check()
+    return out
+
+
+def compare(got, want, dtype, what):
+    """float32: every logit within 1e-4.  bfloat16: per position, the root mean square of the difference (its
+    mean over the vocabulary taken off) against that of the logits themselves: the operands' rounding (2^-9
+    each) reaches the logits of these tiny models at about one part in a hundred, while a key, a window's edge
+    or an expert's weight that is wrong moves a position's logits by their own size.  A token whose two best
+    experts score within rounding of one another may choose the other in bfloat16 (the router is left as
+    drawn), which moves that position alone: two positions in a hundred may lie beyond the bound."""
+    if dtype == "float32":
+        return ru.compare(got, want, dtype, what)
+    rel, where = [], []
+    for name in sorted(got):
+        for position in sorted(got[name]):
+            row, ref = got[name][position], want[name][position]
+            assert np.isfinite(row).all(), f"{what}: {name}[{position}] not finite"
+            d, c = row - ref, ref - ref.mean()
+            rel.append(float(np.sqrt(((d - d.mean()) ** 2).mean()) / np.sqrt((c ** 2).mean())))
+            where.append((name, position))
+    rel = np.array(rel)
+    far = int((rel > 0.25).sum())
+    worst = int(rel.argmax())
+    assert far <= max(1, 0.02 * len(rel)), \
+        f"{what} (bfloat16): {far} of {len(rel)} positions are off, the worst request {where[worst][0]!r} position {where[worst][1]}: {rel[worst]:.3f}"
+    assert np.percentile(rel, 90) <= 0.08, f"{what} (bfloat16): a tenth of the positions is off by {np.percentile(rel, 90):.3f} and more"
+
+
+def test_every_layer_leaves_the_stream_the_plain_layers_leave(model):
+    """The residual stream after every layer, float32."""
+    from tokenizer_b200.engine import Engine, StepEntry
+    folder, cfg, page, requests, _ = model
+    ids = max(requests.values(), key=len)
+    raw, w = plain.load_folder(folder)
+    want = []
+    plain.forward(raw, w, ids, want)
+    engine = Engine.from_folder(folder, dtype="float32", num_pages=-(-len(ids) // page) + 1, page_size=page,
+                                max_requests=1, use_graphs=False)
+    got = []
+    for block in set(engine.model.blocks):
+        def run(stream, ctx, cache, inner=block.forward):
+            inner(stream, ctx, cache)
+            got.append(stream.flush().clone())
+        block.forward = run
+    cache = engine.cache.open("r")
+    engine.cache.reserve(cache, len(ids))
+    engine.step([StepEntry(cache, ids, [0])])
+    assert len(got) == len(want) == len(cfg.layers)
+    for at, (a, b) in enumerate(zip(got, want)):
+        err, size = float((a.cpu()[:len(ids)] - b.float()).abs().max()), float(b.abs().max())
+        assert err <= 1e-4 * max(1.0, size), f"the stream after layer {at}: {err:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_prompts(model, dtype):
+    folder, cfg, page, requests, want = model
+    steps = ru.steps_whole(requests)
+    budget = max(ru.rounded64(len(v)) for v in requests.values())
+    got = ru.collect(steps, replay(folder, dtype, steps, budget, page))
+    assert {k: len(v) for k, v in got.items()} == {k: len(v) for k, v in requests.items()}
+    compare(got, want, dtype, "whole")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompt_then_token_by_token(model, dtype):
+    """The last 60 tokens one by one: more than the windows of 1, 24 and 50 keys and the chunks of 1, 7, 10, 20 and
+    21 positions, so that edges pass under decoded tokens and pages behind them are given back."""
+    folder, cfg, page, requests, want = model
+    steps = ru.steps_decode_tail(requests, 60)
+    budget = max(ru.rounded64(len(v)) for v in requests.values())
+    got = ru.collect(steps, replay(folder, dtype, steps, budget, page))
+    compare(got, want, dtype, "decode tail")
+
+
+def test_every_token_alone_from_the_first(model):
+    """A sequence fed one token a step from its very first: the first token sees itself alone."""
+    folder, cfg, page, requests, want = model
+    some = {k: v for k, v in requests.items() if len(v) <= 50}
+    steps = ru.steps_portions(some, (1,))
+    budget = max(ru.rounded64(len(v)) for v in some.values())
+    got = ru.collect(steps, replay(folder, "float32", steps, budget, page))
+    ru.compare(got, {k: want[k] for k in some}, "float32", "token by token from the start")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("sizes", [(2, 7, 3, 16, 2, 33, 5, 2, 64, 9), (2,), (31, 1, 1, 96)])
+def test_portions(model, dtype, sizes):
+    folder, cfg, page, requests, want = model
+    if sizes == (2,):
+        requests = {k: v for k, v in requests.items() if len(v) <= 100}
+    steps = ru.steps_portions(requests, sizes)
+    budget = max(ru.rounded64(len(v)) for v in requests.values())
+    got = ru.collect(steps, replay(folder, dtype, steps, budget, page))
+    assert {k: len(v) for k, v in got.items()} == {k: len(v) for k, v in requests.items()}
+    compare(got, want, dtype, f"portions {sizes}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("live", [4, 2])
+def test_mixed_batches_on_pages_and_slots_that_are_used_again(model, dtype, live):
+    folder, cfg, page, requests, want = model
+    steps, peak = ru.steps_mixed(requests, max_live=live, seed=live)
+    assert peak < sum(ru.rounded64(len(v)) for v in requests.values()) and len(requests) > live
+    got = ru.collect(steps, replay(folder, dtype, steps, peak, page, max_requests=live))
+    assert {k: len(v) for k, v in got.items()} == {k: len(v) for k, v in requests.items()}
+    compare(got, want, dtype, "mixed")
+
+
+def test_sizes_that_tiny_models_make_equal_or_one(tmp_path_factory):
+    """One layer of each kind with one head, one key/value head, one expert of which one is used, a window and a
+    chunk of two, two rotated lanes; and a model whose every layer but the first borrows the first's keys."""
+    from tiny_zobelorn import chunked, config, dense, moe, windowed
+    from tokenizer_b200 import write_random_model
+    ones = config([windowed(1, 1, 16, 16, 0.25, size=2, rot=(10.0, 2, 1.0), softcap=1.0, mlp=moe(1, 1, 8)),
+                   chunked(1, 1, 8, 8, 0.35, size=2, rot=(10.0, 2, (2.0, 1.0, 2.0, 8)), mlp=moe(2, 1, 8, shared=8))],
+                  vocab=40, width=16, eps=1e-6, scale=1.0, mult=1.0)
+    bands = (8.0, 1.0, 4.0, 128)
+    borrowers = config([chunked(4, 2, 32, 32, 0.18, size=48, rot=(1000.0, 32, bands), mlp=dense(48))] +
+                       [chunked(4, 2, 32, 32, 0.18, size=48 // (i + 1), rot=(1000.0, 32, bands), kv_from=0, mlp=dense(24))
+                        for i in range(3)], vocab=90, width=48, eps=1e-6, scale=2.0, mult=0.6)
+    for at, cfg in enumerate((ones, borrowers)):
+        folder, page = str(tmp_path_factory.mktemp(f"zobelorn_more{at}")), 16
+        write_random_model(folder, cfg, 11 + at, scale=SHARPEN)
+        requests = {f"r{i}": random_ids(n, cfg.vocab, 500 + i) for i, n in enumerate([2, 70, 35, 141, 18, 66])}
+        want = reference_logits(folder, requests)
+        steps = ru.steps_whole(requests)
+        got = ru.collect(steps, replay(folder, "float32", steps, max(ru.rounded64(len(v)) for v in requests.values()), page))
+        ru.compare(got, want, "float32", f"model {at}, whole")
+        steps, peak = ru.steps_mixed(requests, max_live=3, seed=5)
+        got = ru.collect(steps, replay(folder, "float32", steps, peak, page, max_requests=3))
+        ru.compare(got, want, "float32", f"model {at}, mixed")
+
+
+def test_steps_launched_anew_agree_with_replayed_ones(model):
+    folder, cfg, page, requests, want = model
+    steps, peak = ru.steps_mixed(requests, max_live=3, seed=5)
+    got = ru.collect(steps, replay(folder, "float32", steps, peak, page, max_requests=3, use_graphs=False))
+    ru.compare(got, want, "float32", "without graphs")
+
+
+def test_replay_program_drives_the_same_engine(model, tmp_path):
+    folder, cfg, page, requests, want = model
+    steps, peak = ru.steps_mixed(requests, max_live=3, seed=9)
+    out = ru.run_trace(folder, "float32", steps, str(tmp_path), peak, page)
+    ru.compare(ru.collect(steps, out), want, "float32", "the replay program")
+
+
+# ---- generation ---------------------------------------------------------------------------------------
+def near_best(cfg, w, prompt, tokens, dtype):
+    logits = plain.forward(cfg, w, list(prompt) + list(tokens)).float()
+    lead = logits[len(prompt) - 1:-1]
+    chosen = lead.gather(1, torch.tensor(tokens)[:, None])[:, 0]
+    slack = 1e-4 if dtype == "float32" else 0.1 * float(logits.abs().max())
+    gap = lead.max(dim=1).values - chosen
+    assert float(gap.max()) <= slack, f"token {int(gap.argmax())} lies {float(gap.max())} below the best logit"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_entry_point(model, dtype):
+    import tokenizer_b200 as tb
+    folder, cfg, page, requests, _ = model
+    raw, w = plain.load_folder(folder)
+    engine_model = tb.load_model(folder, dtype=dtype)
+    for n in (1, 9, 70):
+        prompt = random_ids(n, cfg.vocab, 500 + n)
+        out = tb.generate(engine_model, prompt, tb.GenerateParams.greedy(24))
+        assert out.reason == tb.StopReason.MAX_TOKENS and len(out.tokens) == 24
+        near_best(raw, w, prompt, out.tokens, dtype)
+
+
+def test_a_batch_through_the_scheduler_with_preemption_gives_each_request_its_own_ids(model):
+    """Five prompts on a pool that cannot hold them all: requests are preempted and computed again."""
+    import tokenizer_b200 as tb
+    folder, cfg, page, requests, _ = model
+    raw, w = plain.load_folder(folder)
+    engine_model = tb.load_model(folder, dtype="float32")
+    prompts = [random_ids(n, cfg.vocab, 600 + n) for n in (30, 7, 55, 18, 41)]
+    engine = tb.engine_for(engine_model, 192, page_size=page, max_requests=3, share_prefixes=False)
+    results = tb.generate_batch(engine, prompts, tb.GenerateParams.greedy(20), max_batch_size=3, token_budget=48,
+                                page_size=page)
+    for prompt, result in zip(prompts, results):
+        near_best(raw, w, prompt, result.tokens, "float32")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_on_the_device(model, dtype):
+    """300 greedy steps without a visit to the host between them (captured and replayed): windows and chunk edges
+    pass under decoded tokens, pages behind them are given back."""
+    from tokenizer_b200.engine import Engine, StepEntry
+    folder, cfg, page, requests, _ = model
+    raw, w = plain.load_folder(folder)
+    engine = Engine.from_folder(folder, dtype=dtype, num_pages=-(-2 * 384 // page), page_size=page, max_requests=2)
+    prompts = [random_ids(5, cfg.vocab, 700), random_ids(41, cfg.vocab, 701)]
+    caches, first = [], []
+    for i, prompt in enumerate(prompts):
+        c = engine.cache.open(i)
+        engine.cache.reserve(c, len(prompt))
+        first.append(int(engine.step([StepEntry(c, prompt, [len(prompt) - 1])]).argmax()))
+        caches.append(c)
+    history = engine.decode_steps([StepEntry(c, [t], [0]) for c, t in zip(caches, first)], 300)
+    for i, prompt in enumerate(prompts):
+        near_best(raw, w, prompt, [first[i]] + [step[i] for step in history], dtype)
+
+
+def test_the_command_line_generates_from_a_configuration_of_this_design(tmp_path):
+    """`--random-weights config.json` draws the weights the configuration declares; two prompts go through the
+    scheduler and print ids that the plain implementation ranks best."""
+    import json
+    import os
+    import subprocess
+    import sys
+    import tokenizer_b200 as tb
+    cfg, seed, page = TINY["a"]()
+    path = str(tmp_path / "config.json")
+    with open(path, "w") as fh:
+        json.dump(cfg.to_dict(), fh)
+    folder = tb.write_random_model(str(tmp_path / "same"), cfg, 0)        # the command line's default seed
+    raw, w = plain.load_folder(folder)
+    prompts = [random_ids(11, cfg.vocab, 801), random_ids(40, cfg.vocab, 802)]
+    cli = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bin", "qwen-infer")
+    args = [sys.executable, cli, "--random-weights", path, "--weights-seed", "0", "--dtype", "float32",
+            "--max-tokens", "10", "--page-size", str(page)]
+    for prompt in prompts:
+        args += ["--ids", ",".join(str(t) for t in prompt)]
+    proc = subprocess.run(args, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr
+    lines = proc.stdout.strip().splitlines()
+    assert len(lines) == 2
+    for prompt, line in zip(prompts, lines):
+        near_best(raw, w, prompt, [int(t) for t in line.split()], "float32")

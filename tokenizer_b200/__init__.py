@@ -2,7 +2,7 @@
 sm_100a): from a model folder (config.json, model.safetensors) to the next
 token.  See `generate` for the entry point."""
 from . import config
-from .config import ConfigError, KatopelConfig, PufuzenConfig, Qwen2Config, VizonexConfig, load_config, register_architecture
+from .config import ConfigError, KatopelConfig, PufuzenConfig, Qwen2Config, VizonexConfig, ZobelornConfig, load_config, register_architecture
 from .weights import WeightError, write_random_model
 
 from .api import (Control, Engine, Generated, GenerateParams, StopReason, engine_for, generate,
@@ -11,6 +11,6 @@ from .engine.scheduler import Scheduler
 
 __all__ = ["Control", "Engine", "Generated", "GenerateParams", "StopReason", "engine_for",
            "generate", "generate_batch", "generate_with", "greedy_tokens", "load_eos_token_ids",
-           "load_model", "random_model", "Scheduler", "ConfigError", "KatopelConfig", "PufuzenConfig", "Qwen2Config", "VizonexConfig", "WeightError", "load_config", "register_architecture",
+           "load_model", "random_model", "Scheduler", "ConfigError", "KatopelConfig", "PufuzenConfig", "Qwen2Config", "VizonexConfig", "ZobelornConfig", "WeightError", "load_config", "register_architecture",
            "write_random_model"]
 __version__ = "0.1.0"

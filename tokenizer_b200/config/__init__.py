@@ -5,9 +5,10 @@ from .qwen2 import Qwen2Config
 from .pufuzen import PufuzenConfig
 from .katopel import KatopelConfig
 from .vizonex import VizonexConfig
+from .zobelorn import ZobelornConfig
 
 __all__ = [
-    "ConfigError", "KatopelConfig", "LayerCall", "LayerSpec", "ModelSpec", "PartSpec", "PufuzenConfig", "Qwen2Config", "VizonexConfig",
+    "ConfigError", "KatopelConfig", "LayerCall", "LayerSpec", "ModelSpec", "PartSpec", "PufuzenConfig", "Qwen2Config", "VizonexConfig", "ZobelornConfig",
     "config_class_for", "config_from_dict", "load_config", "register_architecture",
     "registered_architectures",
 ]

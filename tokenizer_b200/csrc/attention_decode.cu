@@ -115,7 +115,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const int* __restrict__ row_req, const int* __restrict__ pos, int nh,
                         int nkv, int page, int window, int key_chunk, float scale,
                         float* __restrict__ scratch, int* __restrict__ counters, int min_chunk,
-                        const int* __restrict__ rows, const float* __restrict__ sink) {
+                        const int* __restrict__ rows, const float* __restrict__ sink, float softcap) {
   extern __shared__ __align__(16) unsigned char dec_smem[];
   __shared__ int is_last;
   // The rows' requests, positions and block tables were written before the predecessor (the
@@ -256,6 +256,9 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 #pragma unroll
   for (int i = 0; i < HEAD_DIM / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   const float scale_log2 = scale * 1.4426950408889634f;
+  // with a cap, a score in the exponential's base: cap * log2(e) * tanh(raw * scale / cap)
+  const bool capped = softcap > 0.f;
+  const float cap_in = capped ? scale / softcap : 0.f, cap_out = softcap * 1.4426950408889634f;
   if (have_tile && !early) {
     slots_now = tile_slots(k_mine);
     if (kVBuffers == 2) stage_values(slots_now, v_buf);
@@ -300,7 +303,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          s[nt][e] *= scale_log2;
+          s[nt][e] = capped ? softcap_raw(s[nt][e], cap_in, cap_out) : s[nt][e] * scale_log2;
           m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nt][e]);
         }
       }
@@ -310,7 +313,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int key = k0 + nt * 8 + 2 * t + (e & 1);
-          s[nt][e] = key <= last ? s[nt][e] * scale_log2 : -INFINITY;
+          s[nt][e] = key <= last ? (capped ? softcap_raw(s[nt][e], cap_in, cap_out) : s[nt][e] * scale_log2) : -INFINITY;
           m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nt][e]);
         }
       }
@@ -498,7 +501,7 @@ TOKB200_API int tokb200_decode_attention(
     const void* q, const void* k_pool, const void* v_pool, void* out, const int* block_table,
     int table_stride, const int* row_req, const int* pos, int n_rows, int nh, int nkv, int d,
     int page, int window, int key_chunk, float scale, float* scratch, int* counters, const int* rows,
-    const float* sink, cudaStream_t stream) {
+    const float* sink, float softcap, cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
   if (d != HEAD_DIM || nh <= 0 || nkv <= 0 || nh % nkv || nh / nkv > DEC_MAX_GROUP || page <= 0 ||
       nkv > 65535 || n_rows > 65535)
@@ -572,7 +575,7 @@ TOKB200_API int tokb200_decode_attention(
   const bool alias = k_pool == v_pool && kVBuffers == 2;
   void (*kernel)(const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*, __nv_bfloat16*, const int*,
                  int, const int*, const int*, int, int, int, int, int, float, float*, int*, int, const int*,
-                 const float*) =
+                 const float*, float) =
       alias ? (early ? (cluster ? decode_attention_kernel<true, true, true> : decode_attention_kernel<false, true, true>)
                      : (cluster ? decode_attention_kernel<true, false, true> : decode_attention_kernel<false, false, true>))
             : (early ? (cluster ? decode_attention_kernel<true, true, false> : decode_attention_kernel<false, true, false>)
@@ -593,7 +596,7 @@ TOKB200_API int tokb200_decode_attention(
                             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                             (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table,
                             table_stride, row_req, pos, nh, nkv, page, window, key_chunk, scale, scratch,
-                            counters, min_chunk, rows, sink);
+                            counters, min_chunk, rows, sink, softcap);
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = dim3(DEC_THREADS);
@@ -615,6 +618,6 @@ TOKB200_API int tokb200_decode_attention(
   cudaError_t err = cudaLaunchKernelEx(&config, kernel, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                                        (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table,
                                        table_stride, row_req, pos, nh, nkv, page, window, key_chunk, scale, scratch,
-                                       counters, min_chunk, rows, sink);
+                                       counters, min_chunk, rows, sink, softcap);
   return err == cudaSuccess ? TOKB200_OK : (int)err;
 }

@@ -13,7 +13,8 @@
 //
 // `sink` (optional, one float32 per query head): a learned score without key or value that
 // takes part in the softmax's denominator once, unscaled: the running maximum starts at it
-// and the running sum at 1.
+// and the running sum at 1.  `softcap` (> 0): a score s becomes softcap * tanh(s / softcap) before
+// the softmax.
 #include "common.cuh"
 
 #define ATT_THREADS 128
@@ -27,7 +28,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                const int* __restrict__ block_table, int table_stride,
                                const int* __restrict__ row_req, const int* __restrict__ pos,
                                int nh, int nkv, int d, int page, int window, int chunk, float scale,
-                               const float* __restrict__ sink) {
+                               const float* __restrict__ sink, float softcap) {
   extern __shared__ float smem[];
   float* q_s = smem;                 // d
   float* p_s = smem + d;             // ATT_CHUNK
@@ -62,6 +63,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
       float dot = 0.f;
       for (int i = 0; i < d; ++i) dot += q_s[i] * to_float(k_row[i]);
       s = dot * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
     }
     const float c_max = block_max(s, scratch);
     const float m_new = fmaxf(m, c_max);
@@ -97,7 +99,7 @@ TOKB200_API int tokb200_paged_attention_generic(
     const void* q, const void* k_pool, const void* v_pool, void* out, int dtype,
     const int* block_table, int table_stride, const int* row_req, const int* pos, int n_rows,
     int nh, int nkv, int d, int page, int window, int chunk, float scale, const float* sink,
-    cudaStream_t stream) {
+    float softcap, cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
   if (d <= 0 || d > ATT_MAX_HEAD_DIM || nh <= 0 || nkv <= 0 || nh % nkv || page <= 0 ||
       nh > 65535)
@@ -107,12 +109,12 @@ TOKB200_API int tokb200_paged_attention_generic(
   if (dtype == TOKB200_F32)
     paged_attention_generic_kernel<float><<<grid, ATT_THREADS, smem, stream>>>(
         (const float*)q, (const float*)k_pool, (const float*)v_pool, (float*)out, block_table,
-        table_stride, row_req, pos, nh, nkv, d, page, window, chunk, scale, sink);
+        table_stride, row_req, pos, nh, nkv, d, page, window, chunk, scale, sink, softcap);
   else if (dtype == TOKB200_BF16)
     paged_attention_generic_kernel<__nv_bfloat16><<<grid, ATT_THREADS, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
         (__nv_bfloat16*)out, block_table, table_stride, row_req, pos, nh, nkv, d, page, window,
-        chunk, scale, sink);
+        chunk, scale, sink, softcap);
   else
     return TOKB200_BAD_DTYPE;
   return tokb200_launch_status();

@@ -106,7 +106,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ row_req, const int* __restrict__ pos,
                          const int* __restrict__ tiles, int n_tiles, int nh, int nkv, int page,
-                         int window, int chunk, float scale_log2, const float* __restrict__ sink) {
+                         int window, int chunk, float scale_log2, const float* __restrict__ sink,
+                         float cap_in, float cap_out) {
   extern __shared__ __align__(16) __nv_bfloat16 smem[];
   __nv_bfloat16* q_s = smem;                       // [64][kStride]
   __nv_bfloat16* k_s = q_s + kTile;                // PF_STAGES tiles
@@ -211,6 +212,15 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
           mma16816(s[2 * np], q_frag[ks], kf[ks & 1][np][0], kf[ks & 1][np][1]);
           mma16816(s[2 * np + 1], q_frag[ks], kf[ks & 1][np][2], kf[ks & 1][np][3]);
         }
+      }
+    }
+    // ---- a cap on the scores (cap_in > 0): the raw product is squashed so that, times the scale,
+    // it is cap * tanh(score / cap)
+    if (cap_in > 0.f) {
+#pragma unroll
+      for (int nt = 0; nt < PF_KEYS / 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[nt][e] = softcap_raw(s[nt][e], cap_in, cap_out);
       }
     }
     // ---- mask (only in blocks that reach past a row's position or before its window),
@@ -318,7 +328,8 @@ TOKB200_API int tokb200_prefill_attention_head_dim() { return HEAD_DIM; }
 TOKB200_API int tokb200_prefill_attention(
     const void* q, const void* k_pool, const void* v_pool, void* out, const int* block_table,
     int table_stride, const int* row_req, const int* pos, const int* tiles, int n_tiles, int nh,
-    int nkv, int d, int page, int window, int chunk, float scale, const float* sink, cudaStream_t stream) {
+    int nkv, int d, int page, int window, int chunk, float scale, const float* sink, float softcap,
+    cudaStream_t stream) {
   if (n_tiles <= 0) return TOKB200_OK;
   if (d != HEAD_DIM || nh <= 0 || nkv <= 0 || nh % nkv || page <= 0 || nh > 65535)
     return TOKB200_BAD_SIZE;
@@ -339,6 +350,6 @@ TOKB200_API int tokb200_prefill_attention(
   prefill_attention_kernel<<<grid, PF_THREADS, smem, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
       (__nv_bfloat16*)out, block_table, table_stride, row_req, pos, tiles, n_tiles, nh, nkv, page,
-      window, chunk, scale_log2, sink);
+      window, chunk, scale_log2, sink, softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap / scale : 0.f);
   return tokb200_launch_status();
 }

@@ -201,7 +201,8 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ row_req, const int* __restrict__ pos,
                          const int* __restrict__ tiles, int n_tiles, int nh, int nkv, int page, int window,
-                         int chunk, float scale_log2, const float* __restrict__ sink) {
+                         int chunk, float scale_log2, const float* __restrict__ sink, float cap_in,
+                         float cap_out) {
   extern __shared__ __align__(1024) unsigned char fa_raw[];      // swizzle atoms: 1024-byte aligned
   unsigned char* q_s = fa_raw;
   unsigned char* k_s = q_s + kQBytes;                            // FA_KV_BUFFERS buffers
@@ -383,6 +384,10 @@ attention_tcgen05_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
       for (int c0 = 0; c0 < kSplitKeys; c0 += 32)
         fa_tmem_load32(tmem_base + lane_base + (unsigned)((b & 1) * 128 + split * kSplitKeys + c0),
                        *reinterpret_cast<float(*)[32]>(&s[c0]));
+      if (cap_in > 0.f) {      // a cap on the scores: times the scale, the squashed raw product is cap * tanh(score / cap)
+#pragma unroll
+        for (int j = 0; j < kSplitKeys; ++j) s[j] = softcap_raw(s[j], cap_in, cap_out);
+      }
       const bool needs_mask = kb + kSplitKeys - 1 > pos0 || kb < lo_last;
       float m_blk = -INFINITY;
       if (needs_mask) {
@@ -529,7 +534,8 @@ TOKB200_API int tokb200_attention_tcgen05_error(void) {
 TOKB200_API int tokb200_attention_tcgen05(
     const void* q, const void* k_pool, const void* v_pool, void* out, const int* block_table,
     int table_stride, const int* row_req, const int* pos, const int* tiles, int n_tiles, int nh,
-    int nkv, int d, int page, int window, int chunk, float scale, const float* sink, cudaStream_t stream) {
+    int nkv, int d, int page, int window, int chunk, float scale, const float* sink, float softcap,
+    cudaStream_t stream) {
   if (n_tiles <= 0) return TOKB200_OK;
   if (d != HEAD_DIM || nh <= 0 || nkv <= 0 || nh % nkv || page <= 0)
     return TOKB200_BAD_SIZE;
@@ -556,5 +562,6 @@ TOKB200_API int tokb200_attention_tcgen05(
                           (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                           (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table, table_stride,
                           row_req, pos, tiles, n_tiles, nh, nkv, page, window, chunk,
-                          scale * 1.4426950408889634f, sink);
+                          scale * 1.4426950408889634f, sink, softcap > 0.f ? scale / softcap : 0.f,
+                          softcap > 0.f ? softcap / scale : 0.f);
 }

@@ -173,6 +173,16 @@ __device__ __forceinline__ int first_visible_key(int p, int window, int chunk) {
   return lo;
 }
 
+// Scores squashed into (-cap, cap) before the softmax: cap * tanh(score / cap).  The kernels on tensor
+// cores keep raw products q . k and fold the score's scale into the exponential, so they squash the raw
+// product: softcap_raw(raw, scale / cap, cap / scale) times the scale is cap * tanh(raw * scale / cap).
+// tanh as 1 - 2 / (exp(2x) + 1) on the fast exponential and division (absolute error about 1e-7, far
+// below a bfloat16 product's own rounding; exp(2x) = inf gives 1, 0 gives -1); the 32-bit path uses tanhf.
+__device__ __forceinline__ float tanh_fast(float x) { return 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f); }
+__device__ __forceinline__ float softcap_raw(float raw, float cap_in, float cap_out) {
+  return cap_out * tanh_fast(raw * cap_in);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -5,6 +5,8 @@
 //   layer_norm          out = LN(x) (optionally of gathered rows)
 //   post_norm_add       x += LN_post(y);  optionally out = LN_next(x): the norm on a sublayer's output,
 //                       the residual add and the norm in front of the next sublayer in one pass
+//                       (`rms` / `next_rms`: that norm is the RMS form instead, y / sqrt(mean(y^2) + eps) * gain,
+//                       with a bias only where one is given)
 //   scaled_sum          out = s1 y1 + s2 y2
 //   stream_inject       x += other + vector: what a pass of a looped stack adds before its first layer
 //
@@ -38,10 +40,12 @@ __device__ __forceinline__ float ln_term(const LnTerm& t, size_t at) {
 
 // mean and 1 / sqrt(var + eps) of the row's n values, which the caller hands over through `get`
 template <typename F>
-__device__ __forceinline__ void ln_statistics(F get, int n, float eps, float* scratch, float& mean, float& inv) {
+__device__ __forceinline__ void ln_statistics(F get, int n, float eps, float* scratch, float& mean, float& inv,
+                                              int rms = 0) {
   float s = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) s += get(i);
-  mean = block_sum(s, scratch) / (float)n;
+  if (!rms)
+    for (int i = threadIdx.x; i < n; i += blockDim.x) s += get(i);
+  mean = rms ? 0.f : block_sum(s, scratch) / (float)n;      // the RMS form takes no mean off
   float q = 0.f;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const float d = get(i) - mean;
@@ -97,7 +101,8 @@ template <typename TO>
 __global__ void __launch_bounds__(1024)
 post_norm_add_kernel(float* __restrict__ x, LnTerm t1, LnTerm t2, const float* __restrict__ gain,
                      const float* __restrict__ bias, float eps, const float* __restrict__ next_gain,
-                     const float* __restrict__ next_bias, float next_eps, TO* __restrict__ out, int hidden) {
+                     const float* __restrict__ next_bias, float next_eps, TO* __restrict__ out, int hidden,
+                     int rms, int next_rms) {
   __shared__ float scratch[33];
   pdl_wait();
   pdl_launch();
@@ -115,7 +120,7 @@ post_norm_add_kernel(float* __restrict__ x, LnTerm t1, LnTerm t2, const float* _
       xv[e] = i < hidden ? xr[i] : 0.f;
       s += v[e];
     }
-    const float mean = block_sum(s, scratch) / (float)hidden;
+    const float mean = rms ? 0.f : block_sum(s, scratch) / (float)hidden;
     float q = 0.f;
 #pragma unroll
     for (int e = 0; e < LN_PER_THREAD; ++e) {
@@ -129,13 +134,13 @@ post_norm_add_kernel(float* __restrict__ x, LnTerm t1, LnTerm t2, const float* _
     for (int e = 0; e < LN_PER_THREAD; ++e) {
       const int i = threadIdx.x + e * blockDim.x;
       if (i < hidden) {
-        xv[e] += (v[e] - mean) * inv * gain[i] + bias[i];
+        xv[e] += (v[e] - mean) * inv * gain[i] + (bias ? bias[i] : 0.f);
         xr[i] = xv[e];
         s += xv[e];
       }
     }
     if (out == nullptr) return;
-    const float mean2 = block_sum(s, scratch) / (float)hidden;
+    const float mean2 = next_rms ? 0.f : block_sum(s, scratch) / (float)hidden;
     q = 0.f;
 #pragma unroll
     for (int e = 0; e < LN_PER_THREAD; ++e) {
@@ -148,20 +153,20 @@ post_norm_add_kernel(float* __restrict__ x, LnTerm t1, LnTerm t2, const float* _
 #pragma unroll
     for (int e = 0; e < LN_PER_THREAD; ++e) {
       const int i = threadIdx.x + e * blockDim.x;
-      if (i < hidden) o[i] = from_float<TO>((xv[e] - mean2) * inv2 * next_gain[i] + next_bias[i]);
+      if (i < hidden) o[i] = from_float<TO>((xv[e] - mean2) * inv2 * next_gain[i] + (next_bias ? next_bias[i] : 0.f));
     }
     return;
   }
   float mean, inv;
-  ln_statistics([&](int i) { return ln_term(t1, base + i) + ln_term(t2, base + i); }, hidden, eps, scratch, mean, inv);
+  ln_statistics([&](int i) { return ln_term(t1, base + i) + ln_term(t2, base + i); }, hidden, eps, scratch, mean, inv, rms);
   for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-    xr[i] += (ln_term(t1, base + i) + ln_term(t2, base + i) - mean) * inv * gain[i] + bias[i];
+    xr[i] += (ln_term(t1, base + i) + ln_term(t2, base + i) - mean) * inv * gain[i] + (bias ? bias[i] : 0.f);
   if (out == nullptr) return;
   __syncthreads();
-  ln_statistics([&](int i) { return xr[i]; }, hidden, next_eps, scratch, mean, inv);
+  ln_statistics([&](int i) { return xr[i]; }, hidden, next_eps, scratch, mean, inv, next_rms);
   TO* o = out + base;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-    o[i] = from_float<TO>((xr[i] - mean) * inv * next_gain[i] + next_bias[i]);
+    o[i] = from_float<TO>((xr[i] - mean) * inv * next_gain[i] + (next_bias ? next_bias[i] : 0.f));
 }
 
 // ---- rows whose width is whole 8s: eight consecutive elements a thread, 16-byte loads ----
@@ -211,15 +216,16 @@ template <typename TO>
 __global__ void __launch_bounds__(1024)
 post_norm_add_rows8_kernel(float* __restrict__ x, LnTerm t1, LnTerm t2, const float* __restrict__ gain,
                            const float* __restrict__ bias, float eps, const float* __restrict__ next_gain,
-                           const float* __restrict__ next_bias, float next_eps, TO* __restrict__ out, int hidden) {
+                           const float* __restrict__ next_bias, float next_eps, TO* __restrict__ out, int hidden,
+                           int rms, int next_rms) {
   __shared__ float scratch[33];
   // gains and biases are weights: asked for before the wait on the predecessor
   const int i0 = threadIdx.x * 8;
   const bool on = i0 < hidden;
-  float g[8], b[8];
+  float g[8], b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   if (on) {
     ln_load8(gain + i0, g);
-    ln_load8(bias + i0, b);
+    if (bias) ln_load8(bias + i0, b);
   }
   pdl_wait();
   pdl_launch();
@@ -233,7 +239,7 @@ post_norm_add_rows8_kernel(float* __restrict__ x, LnTerm t1, LnTerm t2, const fl
   float s = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) s += v[i];
-  const float mean = block_sum(s, scratch) / (float)hidden;
+  const float mean = rms ? 0.f : block_sum(s, scratch) / (float)hidden;
   float q = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) q += on ? (v[i] - mean) * (v[i] - mean) : 0.f;
@@ -250,9 +256,13 @@ post_norm_add_rows8_kernel(float* __restrict__ x, LnTerm t1, LnTerm t2, const fl
   if (out == nullptr) return;
   if (on) {
     ln_load8(next_gain + i0, g);
-    ln_load8(next_bias + i0, b);
+    if (next_bias) ln_load8(next_bias + i0, b);
+    else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) b[i] = 0.f;
+    }
   }
-  const float mean2 = block_sum(s, scratch) / (float)hidden;
+  const float mean2 = next_rms ? 0.f : block_sum(s, scratch) / (float)hidden;
   q = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) q += on ? (xv[i] - mean2) * (xv[i] - mean2) : 0.f;
@@ -317,9 +327,11 @@ TOKB200_API int tokb200_post_norm_add(float* x, const void* y1, int y1_dtype, in
                                       float y1_scale, const void* y2, int y2_dtype, int y2_partials,
                                       long long y2_stride, float y2_scale, const float* gain, const float* bias,
                                       float eps, const float* next_gain, const float* next_bias, float next_eps,
-                                      void* out, int out_dtype, int n_rows, int hidden, cudaStream_t stream) {
+                                      void* out, int out_dtype, int n_rows, int hidden, int rms, int next_rms,
+                                      cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
   if (hidden <= 0 || y1 == nullptr || y1_partials < 1 || (y2 && y2_partials < 1)) return TOKB200_BAD_SIZE;
+  if ((!rms && bias == nullptr) || (out != nullptr && !next_rms && next_bias == nullptr)) return TOKB200_BAD_SIZE;
   if ((y1_dtype == TOKB200_BF16 && y1_partials != 1) || (y2 && y2_dtype == TOKB200_BF16 && y2_partials != 1))
     return TOKB200_BAD_DTYPE;
   const LnTerm t1 = ln_make_term(y1, y1_dtype, y1_partials, y1_stride, y1_scale);
@@ -331,19 +343,21 @@ TOKB200_API int tokb200_post_norm_add(float* x, const void* y1, int y1_dtype, in
     const int threads8 = ((hidden / 8 + 31) / 32) * 32;
     if (out == nullptr || out_dtype == TOKB200_F32)
       return launch_dependent(post_norm_add_rows8_kernel<float>, dim3(n_rows), dim3(threads8), 0, stream, x, t1, t2,
-                              gain, bias, eps, next_gain, next_bias, next_eps, (float*)out, hidden);
+                              gain, bias, eps, next_gain, next_bias, next_eps, (float*)out, hidden, rms, next_rms);
     if (out_dtype == TOKB200_BF16)
       return launch_dependent(post_norm_add_rows8_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads8), 0, stream, x,
-                              t1, t2, gain, bias, eps, next_gain, next_bias, next_eps, (__nv_bfloat16*)out, hidden);
+                              t1, t2, gain, bias, eps, next_gain, next_bias, next_eps, (__nv_bfloat16*)out, hidden,
+                              rms, next_rms);
     return TOKB200_BAD_DTYPE;
   }
   const int threads = ln_threads(hidden);
   if (out == nullptr || out_dtype == TOKB200_F32)
     return launch_dependent(post_norm_add_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, t1, t2, gain,
-                            bias, eps, next_gain, next_bias, next_eps, (float*)out, hidden);
+                            bias, eps, next_gain, next_bias, next_eps, (float*)out, hidden, rms, next_rms);
   if (out_dtype == TOKB200_BF16)
     return launch_dependent(post_norm_add_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, x, t1, t2,
-                            gain, bias, eps, next_gain, next_bias, next_eps, (__nv_bfloat16*)out, hidden);
+                            gain, bias, eps, next_gain, next_bias, next_eps, (__nv_bfloat16*)out, hidden, rms,
+                            next_rms);
   return TOKB200_BAD_DTYPE;
 }
 

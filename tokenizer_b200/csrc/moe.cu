@@ -15,7 +15,9 @@
 // share[t, e] = s[e] * scale for the chosen, not renormalized.  `shared` = 2: the shared expert's
 // share is one (no gate row).  moe_gate knows a clamped activation (MOE_ACT_CLAMPED_SWISH): with
 // g = min(gate, limit) and u = clamp(up, -limit, limit), g * sigmoid(alpha g) * (u + 1); the shared
-// expert's lanes have a limit of their own.
+// expert's lanes have a limit of their own.  With `on_input` the share multiplies the expert's INPUT instead
+// of its output: the expert's first products are linear in their input, so its inner lanes are
+// f(share * gate) * (share * up), and the down product adds the experts up unweighted.
 #include "common.cuh"
 
 enum : int { MOE_SCORE_SOFTMAX_OF_CHOSEN = 0, MOE_SCORE_SIGMOID = 1 };
@@ -164,7 +166,7 @@ __device__ __forceinline__ float moe_glu(int act, float g, float u, float limit,
 template <typename T>
 __global__ void moe_gate_kernel(const T* __restrict__ gu, const float* __restrict__ share, T* __restrict__ out,
                                 int inner, int experts, int ff, int shared, int act, size_t n, float limit,
-                                float shared_limit, float alpha) {
+                                float shared_limit, float alpha, int on_input) {
   pdl_wait();
   pdl_launch();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -176,7 +178,8 @@ __global__ void moe_gate_kernel(const T* __restrict__ gu, const float* __restric
     float value = 0.f;
     if (w != 0.f) {
       const float g = to_float(gu[t * 2 * inner + c]), u = to_float(gu[t * 2 * inner + inner + c]);
-      value = moe_glu(act, g, u, e < experts ? limit : shared_limit, alpha) * w;
+      const float lim = e < experts ? limit : shared_limit;
+      value = on_input ? moe_glu(act, g * w, u * w, lim, alpha) : moe_glu(act, g, u, lim, alpha) * w;
     }
     out[i] = from_float<T>(value);
   }
@@ -185,7 +188,8 @@ __global__ void moe_gate_kernel(const T* __restrict__ gu, const float* __restric
 // bfloat16, inner and expert widths in whole 8s: eight consecutive lanes (one expert's) a thread
 __global__ void moe_gate_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ share,
                                        __nv_bfloat16* __restrict__ out, int inner, int experts, int ff, int shared,
-                                       int act, size_t n8, float limit, float shared_limit, float alpha) {
+                                       int act, size_t n8, float limit, float shared_limit, float alpha,
+                                       int on_input) {
   pdl_wait();
   pdl_launch();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -206,7 +210,10 @@ __global__ void moe_gate_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, con
       for (int k = 0; k < 4; ++k) {
         const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
         const float lim = e < experts ? limit : shared_limit;
-        h[k] = __floats2bfloat162_rn(moe_glu(act, g.x, u.x, lim, alpha) * w, moe_glu(act, g.y, u.y, lim, alpha) * w);
+        h[k] = on_input ? __floats2bfloat162_rn(moe_glu(act, g.x * w, u.x * w, lim, alpha),
+                                                moe_glu(act, g.y * w, u.y * w, lim, alpha))
+                        : __floats2bfloat162_rn(moe_glu(act, g.x, u.x, lim, alpha) * w,
+                                                moe_glu(act, g.y, u.y, lim, alpha) * w);
       }
       packed = *reinterpret_cast<const uint4*>(h);
     }
@@ -235,7 +242,7 @@ TOKB200_API int tokb200_moe_route(const void* h, int h_dtype, const float* w, in
 
 TOKB200_API int tokb200_moe_gate(const void* gu, const float* share, void* out, int dtype, int n_rows, int inner,
                                  int experts, int ff, int shared, int act, float limit, float shared_limit,
-                                 float alpha, cudaStream_t stream) {
+                                 float alpha, int on_input, cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
   if (inner <= 0 || experts <= 0 || ff <= 0 || (long long)experts * ff > inner || act < 0 || act > MOE_ACT_CLAMPED_SWISH ||
       (!shared && (long long)experts * ff != inner))
@@ -245,15 +252,16 @@ TOKB200_API int tokb200_moe_gate(const void* gu, const float* share, void* out, 
   const dim3 grid((unsigned)(blocks < 8192 ? blocks : 8192));
   if (dtype == TOKB200_F32)
     return launch_dependent(moe_gate_kernel<float>, grid, dim3(256), 0, stream, (const float*)gu, share, (float*)out,
-                            inner, experts, ff, shared, act, n, limit, shared_limit, alpha);
+                            inner, experts, ff, shared, act, n, limit, shared_limit, alpha, on_input);
   if (dtype == TOKB200_BF16 && inner % 8 == 0 && ff % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
     const size_t n8 = n / 8, blocks8 = (n8 + 255) / 256;
     return launch_dependent(moe_gate_bf16x8_kernel, dim3((unsigned)(blocks8 < 65535 ? blocks8 : 65535)), dim3(256), 0,
                             stream, (const __nv_bfloat16*)gu, share, (__nv_bfloat16*)out, inner, experts, ff, shared,
-                            act, n8, limit, shared_limit, alpha);
+                            act, n8, limit, shared_limit, alpha, on_input);
   }
   if (dtype == TOKB200_BF16)
     return launch_dependent(moe_gate_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)gu,
-                            share, (__nv_bfloat16*)out, inner, experts, ff, shared, act, n, limit, shared_limit, alpha);
+                            share, (__nv_bfloat16*)out, inner, experts, ff, shared, act, n, limit, shared_limit, alpha,
+                            on_input);
   return TOKB200_BAD_DTYPE;
 }

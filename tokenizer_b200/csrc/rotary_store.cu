@@ -13,6 +13,16 @@
 // whole q projection (all heads at once) is divided by its root mean square, eps inside the root,
 // and multiplied by q_gain; the same for k.  With `temp` (float32, one a query head): the head's
 // queries are multiplied by it, which multiplies the head's scores.  All of it in 32-bit.
+//
+// `half_layout`: the rotated lanes pair in the half form instead (lane i with lane i + rot_dims / 2, both
+// turned by the angle of frequency i).  `head_norm`: after the rotation every query head and every key
+// head is divided by its own root mean square over its `dim` lanes (`head_eps` inside the root, no gain).
+// A rotation turns pairs and leaves each pair's sum of squares as it was, so a head's mean square is
+// taken of its lanes before the rotation, a warp a head, and kept in shared memory.  `kv_heads` = 0: the
+// projection holds queries only (a layer that reads another layer's cache): nothing is written but q_out.
+//
+// attention_gate: out[t, h, l] *= sigmoid(proj[t, at + h * vdim + l]), l < vdim, on rows of `row` lanes a
+// head: a gate on the heads' outputs that is one more projection of the mixer's input.
 #include "common.cuh"
 
 template <typename TI, typename T>
@@ -22,7 +32,9 @@ __global__ void qkv_rotate_store_kernel(const TI* __restrict__ proj, int ld, int
                                         const int* __restrict__ row_req, T* __restrict__ q_out,
                                         T* __restrict__ k_pool, T* __restrict__ v_pool, int heads, int kv_heads,
                                         int dim, int vdim, int row, const float* __restrict__ q_gain,
-                                        const float* __restrict__ k_gain, float eps, const float* __restrict__ temp) {
+                                        const float* __restrict__ k_gain, float eps, const float* __restrict__ temp,
+                                        int half_layout, int head_norm, float head_eps) {
+  extern __shared__ float head_inv[];       // heads + kv_heads, with `head_norm`
   __shared__ float scratch[33];
   const int t = blockIdx.x;
   const int r = row_req[t];
@@ -45,6 +57,26 @@ __global__ void qkv_rotate_store_kernel(const TI* __restrict__ proj, int ld, int
     if (q_gain != nullptr) q_inv = 1.0f / sqrtf(qs / (float)(heads * dim) + eps);
     if (k_gain != nullptr) k_inv = 1.0f / sqrtf(ks / (float)(kv_heads * dim) + eps);
   }
+  if (head_norm) {                                      // a warp a head: the mean square of its lanes
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int head = warp; head < heads + kv_heads; head += blockDim.x >> 5) {
+      const bool query = head < heads;
+      const float* gain = query ? q_gain : k_gain;
+      const float inv = query ? q_inv : k_inv;
+      const int first = query ? 0 : heads * dim;
+      float sum = 0.f;
+      for (int l = lane; l < dim; l += 32) {
+        const int col = head * dim + l;
+        float v = to_float(in[col]) + (bias ? bias[col] : 0.f);
+        if (gain != nullptr) v = v * inv * gain[col - first];
+        sum = fmaf(v, v, sum);
+      }
+      sum = warp_sum(sum);
+      if (lane == 0) head_inv[head] = 1.0f / sqrtf(sum / (float)dim + head_eps);
+    }
+    __syncthreads();
+  }
+  const int half = rot_dims >> 1;
   for (int i = threadIdx.x; i < lanes; i += blockDim.x) {
     const int head = i / row, l = i % row;
     if (head < heads + kv_heads) {                       // a query or key head: bias, rotation
@@ -58,13 +90,15 @@ __global__ void qkv_rotate_store_kernel(const TI* __restrict__ proj, int ld, int
         value = to_float(in[col]) + (bias ? bias[col] : 0.f);
         if (gain != nullptr) value = value * inv * gain[col - first];
         if (l < rot_dims) {
-          const int mate = col ^ 1;
+          const bool second = half_layout ? l >= half : (l & 1);      // the pair's second lane
+          const int mate = half_layout ? (second ? col - half : col + half) : (col ^ 1);
           float other = to_float(in[mate]) + (bias ? bias[mate] : 0.f);
           if (gain != nullptr) other = other * inv * gain[mate - first];
           float s, c;
-          sincosf((float)p * inv_freq[l >> 1], &s, &c);
-          value = (l & 1) ? value * c + other * s : value * c - other * s;
+          sincosf((float)p * inv_freq[half_layout ? (second ? l - half : l) : (l >> 1)], &s, &c);
+          value = second ? value * c + other * s : value * c - other * s;
         }
+        if (head_norm) value *= head_inv[head];
       }
       if (head < heads) {
         if (temp != nullptr) value *= temp[head];
@@ -89,15 +123,55 @@ TOKB200_API int tokb200_qkv_rotate_store(const void* proj, int proj_dtype, int l
                                          const int* row_req, void* q_out, void* k_pool, void* v_pool,
                                          int out_dtype, int n_rows, int heads, int kv_heads, int dim, int vdim,
                                          int row, const float* q_gain, const float* k_gain, float eps,
-                                         const float* temp, cudaStream_t stream) {
+                                         const float* temp, int half_layout, int head_norm, float head_eps,
+                                         cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
-  if (heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0 || row < dim || row < vdim || rot_dims < 0 ||
+  if (kv_heads == 0 && (slot != nullptr || k_gain != nullptr)) return TOKB200_BAD_SIZE;
+  const size_t smem = head_norm ? (size_t)(heads + kv_heads) * sizeof(float) : 0;
+  if (smem > 40000) return TOKB200_BAD_SIZE;
+  if (heads <= 0 || kv_heads < 0 || dim <= 0 || vdim <= 0 || row < dim || row < vdim || rot_dims < 0 ||
       rot_dims % 2 || rot_dims > dim || (rot_dims > 0 && inv_freq == nullptr))
     return TOKB200_BAD_SIZE;
 #define LAUNCH(TI, T)                                                                                         \
-  return launch_dependent(qkv_rotate_store_kernel<TI, T>, dim3(n_rows), dim3(256), 0, stream, (const TI*)proj, \
-                          ld, at, bias, inv_freq, rot_dims, pos, slot, row_req, (T*)q_out, (T*)k_pool,        \
-                          (T*)v_pool, heads, kv_heads, dim, vdim, row, q_gain, k_gain, eps, temp)
+  return launch_dependent(qkv_rotate_store_kernel<TI, T>, dim3(n_rows), dim3(256), smem, stream,              \
+                          (const TI*)proj, ld, at, bias, inv_freq, rot_dims, pos, slot, row_req, (T*)q_out,   \
+                          (T*)k_pool, (T*)v_pool, heads, kv_heads, dim, vdim, row, q_gain, k_gain, eps, temp, \
+                          half_layout, head_norm, head_eps)
+  if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_F32) LAUNCH(float, float);
+  if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_BF16) LAUNCH(float, __nv_bfloat16);
+  if (proj_dtype == TOKB200_BF16 && out_dtype == TOKB200_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  if (proj_dtype == TOKB200_BF16 && out_dtype == TOKB200_F32) LAUNCH(__nv_bfloat16, float);
+#undef LAUNCH
+  return TOKB200_BAD_DTYPE;
+}
+
+// out: [T, heads * row] in place; proj: [T, ld], the gate's columns at .. (heads * vdim)
+template <typename TI, typename T>
+__global__ void attention_gate_kernel(T* __restrict__ out, const TI* __restrict__ proj, int ld, int at, int heads,
+                                      int vdim, int row, size_t n) {
+  pdl_wait();
+  pdl_launch();
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const int per_row = heads * vdim;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const size_t t = i / per_row;
+    const int c = (int)(i % per_row), head = c / vdim, l = c % vdim;
+    const float g = to_float(proj[t * ld + at + c]);
+    T* o = out + (t * heads + head) * row + l;
+    *o = from_float<T>(to_float(*o) / (1.0f + expf(-g)));
+  }
+}
+
+TOKB200_API int tokb200_attention_gate(void* out, int out_dtype, const void* proj, int proj_dtype, int ld, int at,
+                                       int n_rows, int heads, int vdim, int row, cudaStream_t stream) {
+  if (n_rows <= 0) return TOKB200_OK;
+  if (heads <= 0 || vdim <= 0 || row < vdim || at < 0 || ld < at + heads * vdim) return TOKB200_BAD_SIZE;
+  const size_t n = (size_t)n_rows * heads * vdim;
+  const size_t blocks = (n + 255) / 256;
+  const dim3 grid((unsigned)(blocks < 8192 ? blocks : 8192));
+#define LAUNCH(TI, T)                                                                                          \
+  return launch_dependent(attention_gate_kernel<TI, T>, grid, dim3(256), 0, stream, (T*)out, (const TI*)proj, ld, at, \
+                          heads, vdim, row, n)
   if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_F32) LAUNCH(float, float);
   if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_BF16) LAUNCH(float, __nv_bfloat16);
   if (proj_dtype == TOKB200_BF16 && out_dtype == TOKB200_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);

@@ -315,8 +315,10 @@ def _sink(sink, nh):
 
 
 def paged_attention_generic(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv, d, page,
-                            window, scale, sink: Optional[torch.Tensor] = None, chunk: Optional[int] = None) -> None:
-    """`chunk` (optional): keys are seen inside chunks of that many positions counted from 0 (a
+                            window, scale, sink: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
+                            softcap: Optional[float] = None) -> None:
+    """`softcap` (optional, in every attention kernel): a score s becomes softcap * tanh(s / softcap) before
+    the softmax.  `chunk` (optional): keys are seen inside chunks of that many positions counted from 0 (a
     query sees the keys of its own chunk up to itself).  `sink` (float32, one per query head): a score without key or value that counts once in
     the softmax's denominator, unscaled.  `v_pool` may be `k_pool` itself (values that are the
     leading lanes of the key rows)."""
@@ -327,7 +329,7 @@ def paged_attention_generic(q, k_pool, v_pool, out, block_table, row_req, pos, n
     _check(_lib("attention_generic").tokb200_paged_attention_generic(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _i(_tag(q)), _ptr(block_table),
         _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _i(q.shape[0]), _i(nh), _i(nkv),
-        _i(d), _i(page), _i(-1 if window is None else int(window)), _i(0 if chunk is None else int(chunk)), _f(scale), _sink(sink, nh), _stream()),
+        _i(d), _i(page), _i(-1 if window is None else int(window)), _i(0 if chunk is None else int(chunk)), _f(scale), _sink(sink, nh), _f(softcap or 0.0), _stream()),
         "paged_attention")
 
 
@@ -391,7 +393,7 @@ def decode_attention_supported(nh: int, nkv: int, d: int) -> bool:
 
 def decode_attention(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv, d, page, window,
                      scale, rows: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None,
-                     chunk: Optional[int] = None) -> None:
+                     chunk: Optional[int] = None, softcap: Optional[float] = None) -> None:
     """Attention for rows of one token each (bfloat16): keys are split over
     blocks and merged; the scratch for the pieces is kept per (device, rows,
     heads, head size) and reused by every layer, which run one after another.  With `rows`
@@ -414,7 +416,7 @@ def decode_attention(q, k_pool, v_pool, out, block_table, row_req, pos, nh, nkv,
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
         _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _i(n_rows), _i(nh), _i(nkv), _i(d),
         _i(page), _i(-1 if window is None else int(window)), _i(0 if chunk is None else int(chunk)), _f(scale), _ptr(scratch),
-        _ptr(counters), _ptr(rows), _sink(sink, nh), _stream()), "decode_attention")
+        _ptr(counters), _ptr(rows), _sink(sink, nh), _f(softcap or 0.0), _stream()), "decode_attention")
 
 
 _stream_plans = {}
@@ -542,7 +544,8 @@ def prefill_attention_supported(nh: int, nkv: int, d: int) -> bool:
 
 
 def prefill_attention(q, k_pool, v_pool, out, block_table, row_req, pos, tiles, n_tiles, nh, nkv,
-                      d, page, window, scale, sink: Optional[torch.Tensor] = None, chunk: Optional[int] = None) -> None:
+                      d, page, window, scale, sink: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
+                      softcap: Optional[float] = None) -> None:
     """Attention for portions of prompts (bfloat16).  `tiles` is int32 [n, 2]:
     (first row, rows <= 64) of consecutive rows of one request."""
     if q.dtype != torch.bfloat16:
@@ -554,7 +557,7 @@ def prefill_attention(q, k_pool, v_pool, out, block_table, row_req, pos, tiles, 
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
         _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _ptr(tiles), _i(n_tiles), _i(nh),
         _i(nkv), _i(d), _i(page), _i(-1 if window is None else int(window)), _i(0 if chunk is None else int(chunk)), _f(scale), _sink(sink, nh),
-        _stream()), "prefill_attention")
+        _f(softcap or 0.0), _stream()), "prefill_attention")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
@@ -787,7 +790,8 @@ def attention_tcgen05_supported(nh: int, nkv: int, d: int) -> bool:
 
 
 def attention_tcgen05(q, k_pool, v_pool, out, block_table, row_req, pos, tiles, n_tiles, nh, nkv, d,
-                      page, window, scale, sink: Optional[torch.Tensor] = None, chunk: Optional[int] = None) -> None:
+                      page, window, scale, sink: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
+                      softcap: Optional[float] = None) -> None:
     """Attention for portions of prompts on tcgen05 (bfloat16, head size 64 or 128).
     `tiles` is int32 [n, 2]: (first row, rows <= 128) of consecutive rows of one request."""
     if q.dtype != torch.bfloat16:
@@ -799,7 +803,7 @@ def attention_tcgen05(q, k_pool, v_pool, out, block_table, row_req, pos, tiles, 
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(block_table),
         _i(block_table.shape[1]), _ptr(row_req), _ptr(pos), _ptr(tiles), _i(n_tiles), _i(nh),
         _i(nkv), _i(d), _i(page), _i(-1 if window is None else int(window)), _i(0 if chunk is None else int(chunk)), _f(scale), _sink(sink, nh),
-        _stream()), "attention_tcgen05")
+        _f(softcap or 0.0), _stream()), "attention_tcgen05")
 
 
 def attention_tcgen05_check(d: int) -> None:
@@ -1123,18 +1127,23 @@ def _term(term, like):
 
 
 def post_norm_add(x: torch.Tensor, terms, gain, bias, eps: float, next_gain=None, next_bias=None,
-                  next_eps: float = 0.0, out: Optional[torch.Tensor] = None) -> None:
+                  next_eps: float = 0.0, out: Optional[torch.Tensor] = None, rms: bool = False,
+                  next_rms: bool = False) -> None:
     """x += LN(sum of the scaled terms) * gain + bias in place (x float32 [T, H]; `terms`: one or two
-    (tensor, scale)); with `out`, also out = LN(x) * next_gain + next_bias of the new x."""
+    (tensor, scale)); with `out`, also out = LN(x) * next_gain + next_bias of the new x.  `rms` / `next_rms`:
+    that norm is the RMS form, y / sqrt(mean(y^2) + eps) * gain, and its bias may be None."""
     n_rows, hidden = x.shape
-    if x.dtype != torch.float32 or not 1 <= len(terms) <= 2 or gain.numel() != hidden or bias.numel() != hidden:
+    if x.dtype != torch.float32 or not 1 <= len(terms) <= 2 or gain.numel() != hidden or \
+            (bias is None and not rms) or (bias is not None and bias.numel() != hidden):
         raise ValueError("post_norm_add: x float32 [T, H], one or two terms, gain and bias of H")
-    if out is not None and (next_gain is None or next_bias is None or tuple(out.shape) != (n_rows, hidden)):
+    if out is not None and (next_gain is None or (next_bias is None and not next_rms) or
+                            tuple(out.shape) != (n_rows, hidden)):
         raise ValueError("post_norm_add: the norm behind the add needs gain, bias and out [T, H]")
     args = _term(terms[0], x) + _term(terms[1] if len(terms) > 1 else None, x)
     _check(_lib("layer_norm").tokb200_post_norm_add(
         _ptr(x), *args, _ptr(gain), _ptr(bias), _f(eps), _ptr(next_gain), _ptr(next_bias), _f(next_eps),
-        _ptr(out), _i(_tag(out) if out is not None else F32), _i(n_rows), _i(hidden), _stream()), "post_norm_add")
+        _ptr(out), _i(_tag(out) if out is not None else F32), _i(n_rows), _i(hidden), _i(int(rms)), _i(int(next_rms)),
+        _stream()), "post_norm_add")
 
 
 def scaled_sum(terms, out: torch.Tensor) -> None:
@@ -1245,15 +1254,23 @@ def gdn_out_norm(o: torch.Tensor, gate: torch.Tensor, g_at: int, gain: torch.Ten
 # ---- queries, keys and values with unlike head sizes; routed experts ----
 def qkv_rotate_store(proj: torch.Tensor, at: int, bias, inv_freq, rot_dims: int, pos, slot, row_req, q_out, k_pool,
                      v_pool, heads: int, kv_heads: int, dim: int, vdim: int, row: int, q_gain=None, k_gain=None,
-                     eps: float = 0.0, temp=None) -> None:
+                     eps: float = 0.0, temp=None, layout: str = "interleaved", head_norm_eps: Optional[float] = None) -> None:
     """Bias, interleaved rotation of the first `rot_dims` lanes of every query and key head, and the
     cache write, from `proj`'s columns at .. (q, k, v); rows of `row` lanes a head, zero behind dim
     (queries, keys) and vdim (values).  `slot` None: no cache write.  `q_gain` / `k_gain` (float32, one a
     column of q / of k): the whole q (k) projection of a token is divided by its root mean square (`eps`
     inside the root) and multiplied by the gain first; `temp` (float32, one a query head) multiplies
-    the head's queries."""
+    the head's queries.  `layout` "half": lane i of the rotated lanes pairs with lane i + rot_dims / 2 instead.
+    `head_norm_eps` (a number): after the rotation every query and key head is divided by its own root mean
+    square over its dim lanes, that eps inside the root.  `kv_heads` 0: `proj` holds queries only and nothing
+    but `q_out` is written (`slot`, `k_pool`, `v_pool` None)."""
     n = proj.shape[0]
-    if tuple(q_out.shape) != (n, heads * row) or k_pool.dtype != q_out.dtype or v_pool.dtype != q_out.dtype or \
+    if layout not in ("interleaved", "half"):
+        raise ValueError("qkv_rotate_store: the rotated lanes pair interleaved or by halves")
+    if kv_heads == 0 and (slot is not None or k_gain is not None):
+        raise ValueError("qkv_rotate_store: a projection of queries alone writes no cache rows")
+    if tuple(q_out.shape) != (n, heads * row) or \
+            (kv_heads and (k_pool.dtype != q_out.dtype or v_pool.dtype != q_out.dtype)) or \
             at + heads * dim + kv_heads * (dim + vdim) > proj.shape[1]:
         raise ValueError("qkv_rotate_store: q_out is [T, heads * row] in the cache's type, the columns inside proj")
     for gain, size in ((q_gain, heads * dim), (k_gain, kv_heads * dim), (temp, heads)):
@@ -1262,8 +1279,20 @@ def qkv_rotate_store(proj: torch.Tensor, at: int, bias, inv_freq, rot_dims: int,
     _check(_lib("rotary_store").tokb200_qkv_rotate_store(
         _sliced_ptr(proj), _i(_tag(proj)), _i(_ld(proj)), _i(at), _ptr(bias), _ptr(inv_freq), _i(rot_dims), _ptr(pos),
         _ptr(slot), _ptr(row_req), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _i(_tag(q_out)), _i(n), _i(heads),
-        _i(kv_heads), _i(dim), _i(vdim), _i(row), _ptr(q_gain), _ptr(k_gain), _f(eps), _ptr(temp), _stream()),
+        _i(kv_heads), _i(dim), _i(vdim), _i(row), _ptr(q_gain), _ptr(k_gain), _f(eps), _ptr(temp),
+        _i(int(layout == "half")), _i(int(head_norm_eps is not None)), _f(head_norm_eps or 0.0), _stream()),
         "qkv_rotate_store")
+
+
+def attention_gate(out: torch.Tensor, proj: torch.Tensor, at: int, heads: int, vdim: int, row: int) -> None:
+    """out[t, h, l] *= sigmoid(proj[t, at + h * vdim + l]) for l < vdim, in place; `out` is [T, heads * row]
+    (the heads' outputs on rows of `row` lanes), the gate's pre-activations are columns at .. of `proj`."""
+    n = out.shape[0]
+    if tuple(out.shape) != (n, heads * row) or proj.shape[0] != n or at + heads * vdim > proj.shape[1] or row < vdim:
+        raise ValueError("attention_gate: out is [T, heads * row], the gate's columns lie inside proj")
+    _check(_lib("rotary_store").tokb200_attention_gate(
+        _ptr(out), _i(_tag(out)), _sliced_ptr(proj), _i(_tag(proj)), _i(_ld(proj)), _i(at), _i(n), _i(heads), _i(vdim),
+        _i(row), _stream()), "attention_gate")
 
 
 MOE_SCORES = {"softmax_of_chosen": 0, "sigmoid": 1}
@@ -1296,11 +1325,13 @@ def moe_route(h: torch.Tensor, w: torch.Tensor, experts: int, top: int, shared, 
 
 
 def moe_gate(gu: torch.Tensor, share: torch.Tensor, out: torch.Tensor, experts: int, ff: int, shared: bool,
-             activation: str = "silu", limit: float = 0.0, shared_limit: float = 0.0, alpha: float = 1.0) -> None:
+             activation: str = "silu", limit: float = 0.0, shared_limit: float = 0.0, alpha: float = 1.0,
+             on_input: bool = False) -> None:
     """out[t, c] = act(gu[t, c]) * gu[t, I + c] * share[t, expert of lane c]: lanes 0 .. experts * ff
     are the routed experts' (ff each), the lanes behind the shared expert's.  `activation` is one of
     MOE_ACTIVATIONS; "clamped_swish": with g = min(gate, limit), u = clamp(up, -limit, limit), the lane is
-    g * sigmoid(alpha g) * (u + 1) (`shared_limit` for the shared expert's lanes)."""
+    g * sigmoid(alpha g) * (u + 1) (`shared_limit` for the shared expert's lanes).  `on_input`: the share
+    multiplies the expert's input instead, out[t, c] = act(share * gate) * (share * up)."""
     n, inner = out.shape
     if gu.shape[1] != 2 * inner or gu.dtype != out.dtype or tuple(share.shape) != (n, experts + int(shared)):
         raise ValueError("moe_gate: input [T, 2 I], output [T, I] of one type, shares [T, experts (+ 1)]")
@@ -1308,7 +1339,7 @@ def moe_gate(gu: torch.Tensor, share: torch.Tensor, out: torch.Tensor, experts: 
         raise ValueError(f"moe_gate: activation is one of {', '.join(MOE_ACTIVATIONS)}")
     _check(_lib("moe").tokb200_moe_gate(_ptr(gu), _ptr(share), _ptr(out), _i(_tag(gu)), _i(n), _i(inner), _i(experts),
                                         _i(ff), _i(int(shared)), _i(MOE_ACTIVATIONS[activation]), _f(limit),
-                                        _f(shared_limit), _f(alpha), _stream()), "moe_gate")
+                                        _f(shared_limit), _f(alpha), _i(int(on_input)), _stream()), "moe_gate")
 
 
 # ---- a short convolution across steps; a layer whose sublayers share one norm; learned positions ----

@@ -134,11 +134,13 @@ class PagedAttention:
     want packed with a step, the kernel choice (`attend`) and its say in a captured step's key.
     A mixer that inherits it sets `nh` (query heads), `nkv` (heads of the cache rows), `d` (lanes
     of a cache row's head), `window` (None: all keys), `chunk` (None: no chunks), `scale` and, where its softmax has one,
-    `sink` (float32, one learned score per query head that counts once in the denominator)."""
+    `sink` (float32, one learned score per query head that counts once in the denominator) and `softcap` (scores squashed
+    into (-softcap, softcap) by a tanh)."""
 
     graph_safe = True   # launches depend on device-side metadata only
     sink = None
     chunk = None        # n: keys are seen inside chunks of n positions counted from 0
+    softcap = None      # c: a score s counts as c * tanh(s / c)
 
     def batch_annotations(self):
         return [_TILES, _WIDE_TILES, _LONG_TILES, _LONG_WIDE_TILES, _SINGLES]
@@ -164,7 +166,7 @@ class PagedAttention:
                 ops.decode_attention_supported(self.nh, self.nkv, self.d):
             ops.decode_attention(
                 q, k_pool, v_pool, out, group.block_table, ctx.row_req, ctx.pos,
-                self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, sink=sink, chunk=self.chunk)
+                self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, sink=sink, chunk=self.chunk, softcap=self.softcap)
             return
         wide, tiles = ctx.views.get(_WIDE_TILES.key), ctx.views.get(_TILES.key)
         singles = ctx.views.get(_SINGLES.key)
@@ -175,7 +177,7 @@ class PagedAttention:
             # (keys split over blocks, the group's heads as one tile), the portions to theirs
             ops.decode_attention(
                 q, k_pool, v_pool, out, group.block_table, ctx.row_req, ctx.pos,
-                self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, rows=singles[0], sink=sink, chunk=self.chunk)
+                self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, rows=singles[0], sink=sink, chunk=self.chunk, softcap=self.softcap)
             wide, tiles = ctx.views[_LONG_WIDE_TILES.key], ctx.views[_LONG_TILES.key]
         if _PROMPT_KERNEL == "tcgen05" and q.dtype == torch.bfloat16 and \
                 wide is not None and ctx.max_q_len >= _WIDE_FROM and \
@@ -184,18 +186,18 @@ class PagedAttention:
             ops.attention_tcgen05(
                 q, k_pool, v_pool, out, group.block_table, ctx.row_req, ctx.pos,
                 wide[0], wide[1], self.nh, self.nkv, self.d, group.page_size,
-                self.window, self.scale, sink=sink, chunk=self.chunk)
+                self.window, self.scale, sink=sink, chunk=self.chunk, softcap=self.softcap)
             return
         if q.dtype == torch.bfloat16 and tiles is not None and \
                 ops.prefill_attention_supported(self.nh, self.nkv, self.d):
             ops.prefill_attention(
                 q, k_pool, v_pool, out, group.block_table, ctx.row_req, ctx.pos,
                 tiles[0], tiles[1], self.nh, self.nkv, self.d, group.page_size,
-                self.window, self.scale, sink=sink, chunk=self.chunk)
+                self.window, self.scale, sink=sink, chunk=self.chunk, softcap=self.softcap)
             return
         ops.paged_attention_generic(
             q, k_pool, v_pool, out, group.block_table, ctx.row_req, ctx.pos,
-            self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, sink=sink, chunk=self.chunk)
+            self.nh, self.nkv, self.d, group.page_size, self.window, self.scale, sink=sink, chunk=self.chunk, softcap=self.softcap)
 
 
 class GQAttention(PagedAttention):
@@ -372,20 +374,37 @@ class RotaryGQAttention(PagedAttention):
     and queries fill the first dim lanes, values the first vdim, zeros behind (a zero lane adds
     nothing to a score; a zero value lane meets a zero column of the padded Wo), so that the paged
     kernels, which take one head size, serve both.  `input_stack` / `forward_projected` as for
-    the other mixers that may run side by side."""
+    the other mixers that may run side by side.
+
+    More parameters, each off unless given: `qk_norm` (the whole q and the whole k projection divided by their
+    root mean square, with gains `.q.norm`, `.k.norm`), `head_temperature`, `sink`; the rotation's layout comes
+    with its `position` part (interleaved pairs or halves); `head_norm` (after the rotation every query and key
+    head is divided by its root mean square over dim, `norm_eps` inside the root, no gain); `softcap` (a score s
+    counts as softcap * tanh(s / softcap)); `output_gate` (the heads' outputs are multiplied by sigmoid(Wg h),
+    tensor `.g`, heads * vdim rows; the product rides in the stacked input product); `own_kv` False (the layer
+    has no k and v tensors and is called on an earlier call's cache: it projects, rotates and norms queries
+    only); `cache_chunk` (what the cache manager may give back, where other calls read this cache with chunks of
+    their own: a chunk size that all of theirs divide, or None to keep every page)."""
 
     @staticmethod
     def tensors(spec):
         p, x = spec.params, spec.prefix
         hidden, heads, groups, dim, vdim = p["hidden_size"], p["heads"], p["kv_heads"], p["dim"], p["vdim"]
-        out = [TensorSpec(x + ".q", (heads * dim, hidden)), TensorSpec(x + ".k", (groups * dim, hidden)),
-               TensorSpec(x + ".v", (groups * vdim, hidden)), TensorSpec(x + ".o", (hidden, heads * vdim))]
+        own = p.get("own_kv", True)
+        out = [TensorSpec(x + ".q", (heads * dim, hidden))]
+        if own:
+            out += [TensorSpec(x + ".k", (groups * dim, hidden)), TensorSpec(x + ".v", (groups * vdim, hidden))]
+        out.append(TensorSpec(x + ".o", (hidden, heads * vdim)))
         if p.get("bias", True):
-            out += [TensorSpec(x + ".q.b", (heads * dim,)), TensorSpec(x + ".k.b", (groups * dim,)),
-                    TensorSpec(x + ".v.b", (groups * vdim,))]
+            out.append(TensorSpec(x + ".q.b", (heads * dim,)))
+            if own:
+                out += [TensorSpec(x + ".k.b", (groups * dim,)), TensorSpec(x + ".v.b", (groups * vdim,))]
         if p.get("qk_norm"):
-            out += [TensorSpec(x + ".q.norm", (heads * dim,), "one_plus_normal", 0.1),
-                    TensorSpec(x + ".k.norm", (groups * dim,), "one_plus_normal", 0.1)]
+            out.append(TensorSpec(x + ".q.norm", (heads * dim,), "one_plus_normal", 0.1))
+            if own:
+                out.append(TensorSpec(x + ".k.norm", (groups * dim,), "one_plus_normal", 0.1))
+        if p.get("output_gate"):
+            out.append(TensorSpec(x + ".g", (heads * vdim, hidden)))
         if p.get("head_temperature"):
             out.append(TensorSpec(x + ".temp", (heads,), "one_plus_normal", 0.2))
         if p.get("sink"):
@@ -400,6 +419,12 @@ class RotaryGQAttention(PagedAttention):
         self.dim, self.vdim = int(p["dim"]), int(p["vdim"])
         self.scale = float(p["scale"])
         self.window, self.chunk = p.get("window"), p.get("chunk")
+        self.softcap = float(p["softcap"]) if p.get("softcap") is not None else None
+        self.own_kv = bool(p.get("own_kv", True))
+        self.cache_chunk = p["cache_chunk"] if "cache_chunk" in p else self.chunk
+        self.head_norm = bool(p.get("head_norm"))
+        if self.softcap is not None and self.softcap <= 0:
+            raise ConfigError("a cap on the scores is positive")
         if self.nkv <= 0 or self.nh % self.nkv:
             raise ConfigError(f"{self.nh} query heads is not a multiple of {self.nkv} kv heads")
         if self.chunk is not None and int(self.chunk) < 1:
@@ -412,14 +437,22 @@ class RotaryGQAttention(PagedAttention):
             self.rot_dims = int(self.position.dims)
             if self.rot_dims > self.dim:
                 raise ConfigError(f"{self.rot_dims} rotated lanes do not fit a head of {self.dim}")
-        self._stack = [store.get(x + "." + n) for n in "qkv"]
+        names = "qkv" if self.own_kv else "q"
+        self._stack = [store.get(x + "." + n) for n in names]
+        # the gate's pre-activations are more columns of the stacked product, behind q, k and v
+        self.gate_at = None
+        if p.get("output_gate"):
+            self.gate_at = sum(w.shape[0] for w in self._stack)
+            self._stack.append(store.get(x + ".g"))
         self.bias = None
         if p.get("bias", True):
-            self.bias = runtime.vector(torch.cat([store.get(x + f".{n}.b").to(torch.float32) for n in "qkv"]))
+            self.bias = runtime.vector(torch.cat([store.get(x + f".{n}.b").to(torch.float32) for n in names]))
         self.q_gain = self.k_gain = self.temp = None
         self.norm_eps = float(p.get("norm_eps", 0.0))
         if p.get("qk_norm"):
-            self.q_gain, self.k_gain = runtime.vector(store.get(x + ".q.norm")), runtime.vector(store.get(x + ".k.norm"))
+            self.q_gain = runtime.vector(store.get(x + ".q.norm"))
+            if self.own_kv:
+                self.k_gain = runtime.vector(store.get(x + ".k.norm"))
         if p.get("head_temperature"):
             self.temp = runtime.vector(store.get(x + ".temp"))
         if p.get("sink"):
@@ -438,7 +471,7 @@ class RotaryGQAttention(PagedAttention):
         return torch.cat(self._stack, dim=0), None
 
     def cache_need(self):
-        return CacheNeed(kv=KVNeed(self.nkv, self.row, self.window, chunk=self.chunk))
+        return CacheNeed(kv=KVNeed(self.nkv, self.row, self.window, chunk=self.cache_chunk))
 
     def streamed_weights(self):
         return [self.out.weight] if self.inputs is None else [self.inputs.weight, self.out.weight]
@@ -446,14 +479,21 @@ class RotaryGQAttention(PagedAttention):
     def forward_projected(self, proj, at, ctx, cache, out_scale: float = 1.0):
         if out_scale != 1.0:
             raise ValueError("this mixer's output is scaled by whoever adds it")
+        if self.own_kv != cache.writes:
+            raise ValueError("a layer with keys of its own writes its cache; one without reads an earlier call's")
         group = ctx.groups[cache.group]
         q = self.runtime.empty(ctx.n_tokens, self.nh * self.row)
         ops.qkv_rotate_store(proj, at, self.bias, self.position.inv_freq if self.position is not None else None,
                              self.rot_dims, ctx.pos, group.slots if cache.writes else None, ctx.row_req, q,
-                             cache.k_pool, cache.v_pool, self.nh, self.nkv, self.dim, self.vdim, self.row,
-                             q_gain=self.q_gain, k_gain=self.k_gain, eps=self.norm_eps, temp=self.temp)
+                             cache.k_pool if self.own_kv else None, cache.v_pool if self.own_kv else None, self.nh,
+                             self.nkv if self.own_kv else 0, self.dim, self.vdim, self.row,
+                             q_gain=self.q_gain, k_gain=self.k_gain, eps=self.norm_eps, temp=self.temp,
+                             layout=getattr(self.position, "layout", "interleaved"),
+                             head_norm_eps=self.norm_eps if self.head_norm else None)
         mixed = self.runtime.empty(ctx.n_tokens, self.nh * self.row)
         self.attend(q, mixed, ctx, group, cache)
+        if self.gate_at is not None:
+            ops.attention_gate(mixed, proj, at + self.gate_at, self.nh, self.vdim, self.row)
         return self.out.forward(mixed, partials_ok=True)
 
     def forward(self, h, ctx, cache):

@@ -177,7 +177,9 @@ class RoutedMLP:
     largest choice scores, weights s * `route_scale`, not renormalized); `shared_gate` (False: the shared
     expert counts fully and `.shared.sg` does not exist); `activation` (one of `ops.MOE_ACTIVATIONS`;
     "clamped_swish" with `limit`, `shared_limit` and `alpha`: g = min(gate, limit), u = clamp(up, -limit,
-    limit), g sigmoid(alpha g) (u + 1))."""
+    limit), g sigmoid(alpha g) (u + 1)); `share_on` ("output": an expert's output is multiplied by its weight;
+    "input": its input is, expert(w h), which for products without biases is act(w gate) * (w up) on its inner
+    lanes and an unweighted sum behind the down product)."""
 
     @staticmethod
     def tensors(spec):
@@ -214,6 +216,9 @@ class RoutedMLP:
         self.route_scale = float(p.get("route_scale", 1.0))
         self.limit, self.shared_limit = float(p.get("limit", 0.0)), float(p.get("shared_limit", 0.0))
         self.alpha = float(p.get("alpha", 1.0))
+        self.share_on = p.get("share_on", "output")
+        if self.share_on not in ("output", "input"):
+            raise ConfigError(f"an expert's weight multiplies its output or its input; found {self.share_on}")
         if self.score not in ops.MOE_SCORES:
             raise ConfigError(f"a router scores by one of {', '.join(ops.MOE_SCORES)}; found {self.score}")
         if self.groups < 1 or self.experts % self.groups or not 1 <= self.group_keep <= self.groups or \
@@ -241,7 +246,8 @@ class RoutedMLP:
                       correction=self.correction, groups=self.groups, keep=self.group_keep, scale=self.route_scale)
         act = self.runtime.empty(n, self.inner)
         ops.moe_gate(self.gate_up.forward(h), share, act, self.experts, self.ff, bool(self.shared), self.activation,
-                     limit=self.limit, shared_limit=self.shared_limit, alpha=self.alpha)
+                     limit=self.limit, shared_limit=self.shared_limit, alpha=self.alpha,
+                     on_input=self.share_on == "input")
         return self.down.forward(act, partials_ok=True)
 
 

@@ -17,10 +17,17 @@ def tensor_name(spec) -> str:
 
 class RMSNorm:
     """`gain_scale` (optional): a constant folded into the gain in float32, for a model whose
-    logits are the head's product times a constant (the final norm carries it)."""
+    logits are the head's product times a constant (the final norm carries it), or whose sublayer
+    outputs are normed and multiplied by a constant before they are added (the norm behind the
+    sublayer carries it).  `one_plus` (optional): the tensor holds the gain's offset from one; the gain is
+    1 + w, taken in float32.  As the norm on a sublayer's OUTPUT it offers `add_to`, like the layer
+    norm: x += norm(sum of the output's scaled terms), and the next norm of the new x in the same
+    kernel (`csrc/layer_norm.cu`, the RMS form)."""
 
     @staticmethod
     def tensors(spec):
+        if spec.params.get("one_plus"):
+            return [TensorSpec(tensor_name(spec), (spec.params["size"],), "normal", 0.1)]
         return [TensorSpec(tensor_name(spec), (spec.params["size"],), "one_plus_normal")]
 
     def __init__(self, spec, store, runtime):
@@ -28,12 +35,34 @@ class RMSNorm:
         self.eps = float(spec.params["eps"])
         self.runtime = runtime
         self.gain = runtime.vector(store.get(tensor_name(spec)))
+        if spec.params.get("one_plus"):
+            self.gain = (self.gain + 1.0).contiguous()
         if spec.params.get("gain_scale") is not None:
             self.gain = (self.gain * float(spec.params["gain_scale"])).contiguous()
 
     def folded(self):
         """(gain, eps) for a consumer that computes this norm inside its own kernel."""
         return self.gain, self.eps
+
+    def add_to(self, x, terms, then=None):
+        """x += this norm of the summed terms, in place; with `then` (the norm in front of the next
+        sublayer), returns that norm of the new x: one kernel where `then` can be folded (an RMS norm
+        with `folded`, or a layer norm with `affine`)."""
+        if then is None:
+            ops.post_norm_add(x, terms, self.gain, None, self.eps, rms=True)
+            return None
+        fold, affine = getattr(then, "folded", None), getattr(then, "affine", None)
+        if fold is None and affine is None:
+            ops.post_norm_add(x, terms, self.gain, None, self.eps, rms=True)
+            return then.forward(x)
+        out = self.runtime.empty(x.shape[0], self.size)
+        if fold is not None:
+            gain, eps = fold()
+            ops.post_norm_add(x, terms, self.gain, None, self.eps, gain, None, eps, out, rms=True, next_rms=True)
+        else:
+            gain, bias, eps = affine()
+            ops.post_norm_add(x, terms, self.gain, None, self.eps, gain, bias, eps, out, rms=True)
+        return out
 
     def forward_gated(self, x, gated):
         """x += (y + bias) * sigmoid(pre + pre_bias), then the norm of the new x: one kernel."""

@@ -5,6 +5,8 @@ cosine and sine are float32 tables of `max_positions` rows
 (reference: qwen-infer/src/model.rs:138-172)."""
 from __future__ import annotations
 
+import math
+
 import torch
 
 from ..config.spec import ConfigError
@@ -31,12 +33,47 @@ class RotaryHalfSplit:
         return (self.theta, self.rotary_dim, self.max_positions)
 
 
+def scaled_frequencies(freq, scaling):
+    """The frequencies of a rotation after `scaling` (None: as they are), in float64.
+    {"kind": "linear", factor}: every frequency divided by the factor (positions stretched).
+    {"kind": "bands", factor, low, high, original}: by wavelength l = 2 pi / f: kept where l <
+    original / high, divided by the factor where l > original / low, and in between blended with
+    s = (original / l - low) / (high - low) as (1 - s) f / factor + s f."""
+    if scaling is None:
+        return list(freq)
+    kind, factor = scaling.get("kind"), float(scaling["factor"])
+    if factor <= 0:
+        raise ConfigError("a rotation's scaling factor is positive")
+    if kind == "linear":
+        return [f / factor for f in freq]
+    if kind != "bands":
+        raise ConfigError(f"a rotation's frequencies are scaled linearly or by bands, found {kind!r}")
+    low, high, original = float(scaling["low"]), float(scaling["high"]), float(scaling["original"])
+    if high == low:
+        raise ConfigError("the bands of a rotation's scaling need low and high apart")
+    out = []
+    for f in freq:
+        wavelength = 2.0 * math.pi / f
+        if wavelength < original / high:
+            out.append(f)
+        elif wavelength > original / low:
+            out.append(f / factor)
+        else:
+            s = (original / wavelength - low) / (high - low)
+            out.append((1.0 - s) * f / factor + s * f)
+    return out
+
+
 class RotaryInterleaved:
-    """Rotary position encoding, interleaved form: lane 2i of the rotated lanes pairs with lane
-    2i + 1, i < dims / 2; the pair (u, v) at position p becomes (u cos a - v sin a, v cos a +
-    u sin a), a = float32(p) * f_i, f_i = base^(-2i / dims) computed in float64 and stored in
-    float32.  There are no tables and no longest position: the kernels that rotate take the
-    frequencies and compute sine and cosine of the 32-bit angle themselves."""
+    """Rotary position encoding with computed angles.  Interleaved form (`layout` "interleaved"): lane
+    2i of the rotated lanes pairs with lane 2i + 1, i < dims / 2; half form (`layout` "half", kind
+    `rope_half`): lane i pairs with lane i + dims / 2.  The pair (u, v) at position p becomes
+    (u cos a - v sin a, v cos a + u sin a), a = float32(p) * f_i, f_i = base^(-2i / dims), rescaled
+    where the part has a `scaling` (`scaled_frequencies`), computed in float64 and stored in float32.
+    There are no tables and no longest position: the kernels that rotate take the frequencies and
+    compute sine and cosine of the 32-bit angle themselves."""
+
+    layout = "interleaved"
 
     @staticmethod
     def tensors(spec):
@@ -47,9 +84,15 @@ class RotaryInterleaved:
         self.dims = int(spec.params["dims"])
         if self.dims % 2 or self.dims <= 0 or self.base <= 0:
             raise ConfigError(f"rotary width {self.dims} must be even and positive, the base positive")
-        freq = [self.base ** (-2.0 * i / self.dims) for i in range(self.dims // 2)]
+        freq = scaled_frequencies([self.base ** (-2.0 * i / self.dims) for i in range(self.dims // 2)],
+                                  spec.params.get("scaling"))
         self.inv_freq = torch.tensor(freq, dtype=torch.float64).to(torch.float32).to(runtime.device)
+
+
+class RotaryHalfComputed(RotaryInterleaved):
+    layout = "half"
 
 
 register_part("position", "rope_half_split", RotaryHalfSplit)
 register_part("position", "rope_interleaved", RotaryInterleaved)
+register_part("position", "rope_half", RotaryHalfComputed)
