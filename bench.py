@@ -3,7 +3,7 @@
 weights on one B200.  Prints ONE JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
-                    [--config 0.5b|1.5b-mixed|7b|pufuzen|katopel|vizonex]
+                    [--config 0.5b|1.5b-mixed|7b|pufuzen|katopel|vizonex|zobelorn]
 
 A "step" is one decode step of the whole batch.  `value` is decoded tokens a
 second timed on the device over K steps that never return to the host
@@ -196,12 +196,13 @@ def main():
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=SIZES["num_hidden_layers"])
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--config", default="0.5b", choices=["0.5b", "1.5b-mixed", "7b", "pufuzen", "katopel", "vizonex"],
+    parser.add_argument("--config", default="0.5b", choices=["0.5b", "1.5b-mixed", "7b", "pufuzen", "katopel", "vizonex", "zobelorn"],
                         help="0.5b: the headline line; 7b: the same at Qwen2.5-7B sizes with 8,192-token "
                              "contexts; 1.5b-mixed: 32 requests through the scheduler at Qwen2.5-1.5B sizes; "
                              "pufuzen: prefill and decoding of the Pufuzen design at two widths beside Qwen2 at "
                              "equal width, depth and parameters, and its kernels alone; katopel: the same for the Katopel design; "
-                             "vizonex: the Vizonex design beside the Katopel design at equal width, depth and parameters")
+                             "vizonex: the Vizonex design beside the Katopel design at equal width, depth and parameters; "
+                             "zobelorn: the Zobelorn design beside Qwen2 at equal width, depth, heads and parameters")
     parser.add_argument("--context", type=int, default=8192, help="--config 7b: tokens held before decoding")
     parser.add_argument("--layer-phases", action="store_true",
                         help="print where the time of the whole-layer kernel (TOKB200_LAYER=fused) goes, phase by "
@@ -216,7 +217,7 @@ def main():
     parser.add_argument("--only-decode", action="store_true",
                         help="time the decode steps only and print a short line (for profiling)")
     parser.add_argument("--only-kernels", action="store_true",
-                        help="--config katopel, vizonex: the kernels alone, without the models")
+                        help="--config katopel, vizonex, zobelorn: the kernels alone, without the models")
     parser.add_argument("--only-prefill", action="store_true",
                         help="time the 2,048-token prefill only and print a short line (for profiling)")
     args = parser.parse_args()
@@ -244,6 +245,8 @@ def main():
         return run_katopel(args)
     if args.config == "vizonex":
         return run_vizonex(args)
+    if args.config == "zobelorn":
+        return run_zobelorn(args)
     args.steps = max(1, min(args.steps, NEW_TOKENS - args.warmup - 1))
 
     import torch
@@ -1303,6 +1306,221 @@ def run_vizonex(args):
         "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup, "dtype": "bf16",
         "data": "synthetic: random weights drawn on the device, uniform random token ids",
         "config": {"sizes": VIZONEX_SIZES, "prefill_tokens": PREFILL_TOKENS, "decode_context": context,
+                   "peaks": pk["source"], "hbm_gbs": pk["hbm_gbs"],
+                   "l2": "kernels alone: inputs larger than L2 and a 256 MB write between timed launches"},
+        "models": models, "kernels": kernels}))
+    return 0
+
+
+# ---- the Zobelorn design beside the Qwen2 decoder at equal width, depth, heads and parameter count ----
+ZOBELORN_SIZES = {
+    # width; attention of `heads` over `kv_heads` heads of dim / vdim lanes: the windowed kind (a window of `window`
+    # keys, `rot` rotated lanes, a cap on the scores, a gate on the outputs) and the chunked kind (chunks of `chunk`
+    # positions, whole heads rotated; every other one of them borrows the keys and values of the one before);
+    # experts of which a token uses `top`, and a shared one.  The dense feed-forward's width is chosen so that the
+    # model has the parameters of the Qwen2 model beside it.
+    "1k": dict(width=1024, heads=16, kv_heads=4, dim=64, vdim=64, window=1024, chunk=1024, rot=32, softcap=30.0,
+               experts=8, top=2, expert_ff=704, shared_ff=1408, vocab=32000, layers=8, qwen_inner=2816),
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, chunk=1024, rot=64, softcap=30.0,
+               experts=8, top=2, expert_ff=1408, shared_ff=2816, vocab=32000, layers=8, qwen_inner=5632),
+}
+
+
+def zobelorn_config(z, ff):
+    """Layers in the pattern chunked + dense, windowed + experts, chunked on the first layer's keys + experts,
+    windowed + dense, twice."""
+    import tokenizer_b200 as tb
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": z["shared_ff"]}}
+    heads = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5}
+    windowed = dict(heads, mask={"size": z["window"]}, softcap=z["softcap"],
+                    rot={"base": 1000000.0, "dims": z["rot"], "scaling": {"factor": 8.0}})
+    chunked = dict(heads, mask={"size": z["chunk"]},
+                   rot={"base": 20000.0, "dims": z["dim"], "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 512}})
+    layers = []
+    for i in range(z["layers"]):
+        kind = i % 4
+        if kind == 0:
+            layers.append({"type": "attention_2", "mixer": chunked, "mlp": dense})
+        elif kind == 2:
+            layers.append({"type": "attention_2", "mixer": dict(chunked, kv_from=i - 2), "mlp": moe})
+        else:
+            layers.append({"type": "attention", "mixer": windowed, "mlp": moe if kind == 1 else dense})
+    return tb.config.ZobelornConfig.from_dict({
+        "architecture": "Zobelorn", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+        "embedding": {"scale": 16.0}, "residual_mult": 0.3, "layers": layers})
+
+
+def run_zobelorn(args):
+    """Prefill (one step of 2,048 tokens) and decoding (batch 1 and `--batch`, 2,048-token contexts) of the
+    Zobelorn design at two widths, beside the closest model that was there, the Qwen2 decoder (attention in every
+    layer, nothing recurrent), at the same width, depth and heads; the Zobelorn model's dense feed-forward width
+    is chosen so that both have the same parameters.  Then the design's own kernels alone beside the like kernels
+    of the paths that were there, each on inputs larger than L2, against the measured copy peak; the attention
+    kernels with and without the cap on the scores, against one another."""
+    import torch
+    import tokenizer_b200 as tb
+    from tokenizer_b200.kernels import ops
+    from tokenizer_b200.parts.attention import RowTiles
+    from tokenizer_b200.parts.model import declared_tensors
+
+    torch.cuda.set_device(0)
+    pk = peaks()
+    gen = torch.Generator().manual_seed(99)
+    context, steps = 2048, max(8, min(args.steps, 64))
+    timed = device_timed
+    count = lambda config: sum(int(torch.tensor(t.shape).prod()) for t in declared_tensors(config.model_spec()))
+
+    def qwen_config(z):
+        return tb.Qwen2Config.from_dict(dict(
+            architectures=["Qwen2ForCausalLM"], hidden_act="silu", num_hidden_layers=z["layers"],
+            hidden_size=z["width"], num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"],
+            head_dim=z["dim"], intermediate_size=z["qwen_inner"], vocab_size=z["vocab"], rope_theta=1000000.0,
+            rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=32768, use_sliding_window=False,
+            sliding_window=32768, max_window_layers=z["layers"]))
+
+    models = {}
+    for name, z in ZOBELORN_SIZES.items():
+        if args.only_kernels:
+            break
+        beside = qwen_config(z)
+        base, step = count(zobelorn_config(z, 128)), count(zobelorn_config(z, 256)) - count(zobelorn_config(z, 128))
+        ff = max(1, round((count(beside) - base) / step) + 1) * 128
+        models[name] = {"zobelorn": dict(measure_design(zobelorn_config(z, ff), z["vocab"], args, gen, context, steps), ff=ff),
+                        "qwen2": measure_design(beside, z["vocab"], args, gen, context, steps)}
+
+    # ---- kernels alone: inputs larger than L2, a 256 MB write between the timed launches ----
+    dev = "cuda:0"
+    flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)
+
+    def kernel_time(fn, reps=7):
+        times = []
+        for _ in range(3 + reps):
+            flush.zero_()
+            ms, _ = timed(fn)
+            times.append(ms)
+        return sorted(times[3:])[reps // 2]
+
+    kernels = {}
+
+    def record(name, ms, nbytes, like, flops=None):
+        kernels[name] = {"us": round(ms * 1e3, 1), "gb_s": round(nbytes / (ms / 1e3) / 1e9), "like": like,
+                         "of_measured_copy_peak": round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 2)}
+        if flops is not None:
+            kernels[name]["bf16_tflops"] = round(flops / (ms / 1e3) / 1e12, 1)
+
+    rnd = lambda *shape, dtype=torch.float32: torch.randn(*shape, device=dev, dtype=torch.float32).to(dtype)
+    T, H, I = 8192, 2048, 5632
+    # the norm behind a sublayer, the add and the next norm; beside it the pre-norm path's norm with its pending add
+    x, a16 = rnd(T, H), rnd(T, H, dtype=torch.bfloat16)
+    g1 = torch.ones(H, device=dev)
+    out16 = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    record(f"post_norm_add, RMS form with the next norm, {T} x {H} (bfloat16 term)",
+           kernel_time(lambda: ops.post_norm_add(x, [(a16, 1.0)], g1, None, 1e-6, g1, None, 1e-6, out16, rms=True, next_rms=True)),
+           T * H * (2 + 4 + 4 + 2), "rms_norm with pending add")
+    parts = rnd(2, T, H)
+    record(f"post_norm_add, RMS form with the next norm, {T} x {H} (two float32 partial sums)",
+           kernel_time(lambda: ops.post_norm_add(x, [(parts, 1.0)], g1, None, 1e-6, g1, None, 1e-6, out16, rms=True, next_rms=True)),
+           T * H * (8 + 4 + 4 + 2), "rms_norm with pending add")
+    record(f"rms_norm with pending add, {T} x {H}", kernel_time(lambda: ops.rms_norm(x, g1, 1e-6, out16, delta=a16)),
+           T * H * (4 + 4 + 2 + 2), None)
+    b1 = torch.zeros(H, device=dev)
+    record(f"post_norm_add, layer-norm form with the next norm (Katopel path), {T} x {H}",
+           kernel_time(lambda: ops.post_norm_add(x, [(a16, 1.0)], g1, b1, 1e-6, g1, b1, 1e-6, out16)), T * H * (2 + 4 + 4 + 2), None)
+    del parts
+    # queries, keys and values: both kinds of layer, a layer of queries alone, the Katopel path beside them
+    nh, nkv, d = 16, 4, 128
+    wide = rnd(T, (nh + 2 * nkv) * d + nh * d)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    req = torch.zeros(T, dtype=torch.int32, device=dev)
+    q_out = torch.empty(T, nh * d, dtype=torch.bfloat16, device=dev)
+    k_pool = torch.zeros(T + 64, nkv, d, dtype=torch.bfloat16, device=dev)
+    v_pool = torch.zeros_like(k_pool)
+    qg, kg = torch.ones(nh * d, device=dev), torch.ones(nkv * d, device=dev)
+    freq64 = torch.tensor([1e6 ** (-2.0 * i / 64) for i in range(32)], device=dev)
+    freq128 = torch.tensor([2e4 ** (-2.0 * i / 128) for i in range(64)], device=dev)
+    qkv_bytes = T * (nh + 2 * nkv) * d * (4 + 2)
+    record(f"qkv_rotate_store, whole-projection norms and 64 lanes rotated by halves, {T} tokens, {nh} heads over {nkv} of {d}",
+           kernel_time(lambda: ops.qkv_rotate_store(wide, 0, None, freq64, 64, pos, pos, req, q_out, k_pool, v_pool, nh, nkv, d, d, d,
+                                                    q_gain=qg, k_gain=kg, eps=1e-6, layout="half")), qkv_bytes, "qkv_rotate_store")
+    record(f"qkv_rotate_store, whole heads rotated in pairs and a norm a head, {T} tokens",
+           kernel_time(lambda: ops.qkv_rotate_store(wide, 0, None, freq128, 128, pos, pos, req, q_out, k_pool, v_pool, nh, nkv, d, d,
+                                                    d, head_norm_eps=1e-6)), qkv_bytes, "qkv_rotate_store")
+    record(f"qkv_rotate_store, queries alone with a norm a head, {T} tokens",
+           kernel_time(lambda: ops.qkv_rotate_store(wide, 0, None, freq128, 128, pos, None, req, q_out, None, None, nh, 0, d, d, d,
+                                                    head_norm_eps=1e-6)), T * nh * d * (4 + 2), "qkv_rotate_store")
+    bias = torch.zeros((nh + 2 * nkv) * d, device=dev)
+    record(f"qkv_rotate_store, biases and 64 rotated lanes (Katopel path), {T} tokens",
+           kernel_time(lambda: ops.qkv_rotate_store(wide, 0, bias, freq64, 64, pos, pos, req, q_out, k_pool, v_pool, nh, nkv, d, d, d)),
+           qkv_bytes, None)
+    mixed16 = rnd(T, nh * d, dtype=torch.bfloat16)
+    record(f"attention_gate, {T} tokens x {nh} heads of {d}",
+           kernel_time(lambda: ops.attention_gate(mixed16, wide, (nh + 2 * nkv) * d, nh, d, d)), T * nh * d * (4 + 2 + 2), "silu_gate")
+    experts, ff, top = 8, 512, 2
+    gu = rnd(T, 2 * I, dtype=torch.bfloat16)
+    share = torch.zeros(T, experts + 1, device=dev)
+    act = torch.empty(T, I, dtype=torch.bfloat16, device=dev)
+    h_in = rnd(T, H, dtype=torch.bfloat16)
+    router = rnd(experts, H)
+    record(f"moe_route, sigmoid scores, {top} of {experts} experts, width {H}",
+           kernel_time(lambda: ops.moe_route(h_in, router, experts, top, "one", share, score="sigmoid")), T * H * 2, "moe_route")
+    router9 = rnd(experts + 1, H)
+    share9 = torch.zeros(T, experts + 1, device=dev)
+    record(f"moe_route, softmax of the chosen (Katopel path), width {H}",
+           kernel_time(lambda: ops.moe_route(h_in, router9, experts, top, True, share9)), T * H * 2, None)
+    record(f"moe_gate, weights on the experts' input, {T} x {I} lanes of {experts} experts and a shared one",
+           kernel_time(lambda: ops.moe_gate(gu, share, act, experts, ff, True, on_input=True)), T * I * 6, "moe_gate")
+    record(f"moe_gate, weights on the output (Katopel path), {T} x {I}",
+           kernel_time(lambda: ops.moe_gate(gu, share, act, experts, ff, True)), T * I * 6, None)
+    record(f"silu_gate, {T} x {I}", kernel_time(lambda: ops.silu_gate(gu, act)), T * I * 6, None)
+    del gu, act, wide, mixed16
+    # attention with and without the cap: 8,192-token prompt portions of four requests (the tcgen05 and the mma.sync
+    # kernels), then 64 rows of one token over 8,192 keys (the split-key kernel), 16 heads over 4 of 128 lanes
+    page, n_req, n_keys = 16, 4, 8192
+    pages_each = n_keys // page
+    k_pool = rnd(n_req * n_keys, nkv, d, dtype=torch.bfloat16)
+    v_pool = rnd(n_req * n_keys, nkv, d, dtype=torch.bfloat16)
+    table = torch.arange(n_req * pages_each, dtype=torch.int32, device=dev).view(n_req, pages_each)
+    portion = 2048
+    q = rnd(n_req * portion, nh * d, dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    row_req = torch.arange(n_req, dtype=torch.int32, device=dev).repeat_interleave(portion)
+    pos = (torch.arange(portion, dtype=torch.int32, device=dev) + (n_keys - portion)).repeat(n_req)
+    import numpy as np
+    for kernel, run, rows in (("attention_tcgen05", ops.attention_tcgen05, ops.WIDE_TILE_ROWS),
+                              ("prefill_attention", ops.prefill_attention, ops.PREFILL_TILE_ROWS)):
+        note = RowTiles(rows)
+        words = np.zeros(note.capacity(n_req * portion, n_req), dtype=np.int32)
+        n_tiles = note.fill(words, np.arange(n_req, dtype=np.int32) * portion, np.full(n_req, portion, dtype=np.int32),
+                            np.full(n_req, n_keys - portion, dtype=np.int32), False)
+        tiles = torch.tensor(words, device=dev).view(-1, 2)
+        window = 1023
+        # a row of the portion reads the 1,024 keys of its window: two products of 2 * d a key and head
+        flops = n_req * portion * nh * 1024 * 4 * d
+        for cap in (None, 30.0):
+            record(f"{kernel}, {n_req} portions of {portion} rows, a window of 1,024 keys, " + ("capped" if cap else "no cap"),
+                   kernel_time(lambda: run(q, k_pool, v_pool, out, table, row_req, pos, tiles, n_tiles, nh, nkv, d, page, window,
+                                           d ** -0.5, softcap=cap)), 0, None if cap is None else kernel + ", no cap", flops=flops)
+    rows = 64
+    big_k = rnd(rows * n_keys, nkv, d, dtype=torch.bfloat16)
+    big_v = rnd(rows * n_keys, nkv, d, dtype=torch.bfloat16)
+    table = torch.arange(rows * pages_each, dtype=torch.int32, device=dev).view(rows, pages_each)
+    q1 = rnd(rows, nh * d, dtype=torch.bfloat16)
+    out1 = torch.empty_like(q1)
+    req1 = torch.arange(rows, dtype=torch.int32, device=dev)
+    pos1 = torch.full((rows,), n_keys - 1, dtype=torch.int32, device=dev)
+    for cap in (None, 30.0):
+        record(f"decode_attention, {rows} rows x {n_keys} keys, " + ("capped" if cap else "no cap"),
+               kernel_time(lambda: ops.decode_attention(q1, big_k, big_v, out1, table, req1, pos1, nh, nkv, d, page, None,
+                                                        d ** -0.5, softcap=cap)), rows * n_keys * nkv * d * 4,
+               None if cap is None else "decode_attention, no cap")
+    ops.raise_if_error()
+    print(json.dumps({
+        "metric": "prefill and decode tok/s of the Zobelorn design beside Qwen2 at equal width, depth, heads and parameters",
+        "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup, "dtype": "bf16",
+        "data": "synthetic: random weights drawn on the device, uniform random token ids",
+        "config": {"sizes": ZOBELORN_SIZES, "prefill_tokens": PREFILL_TOKENS, "decode_context": context,
                    "peaks": pk["source"], "hbm_gbs": pk["hbm_gbs"],
                    "l2": "kernels alone: inputs larger than L2 and a 256 MB write between timed launches"},
         "models": models, "kernels": kernels}))

@@ -297,7 +297,8 @@ def test_window_edges_and_the_cap_in_every_attention_kernel(kernel, dtype, heads
     if edge > 1:     # the edge matters: seeing the key just outside would pull head 0 of the planted rows to its value
         open_ = plain_rows(q, dense, row_req, pos, scale, None, None, softcap)
         assert float((open_ - want).abs().max()) > 1.0
-    if softcap and edge > 1:                # the cap matters: without it the planted key inside would take all the weight
+    if softcap and softcap <= 8.0 and edge > 1:     # the cap matters where it lies below the planted score of about 20:
+        # without it the planted key inside would take all the weight
         free = plain_rows(q, dense, row_req, pos, scale, size, chunk, None)
         assert float((free - want).abs().max()) > 0.5
 
