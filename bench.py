@@ -1317,20 +1317,19 @@ ZOBELORN_SIZES = {
     # width; attention of `heads` over `kv_heads` heads of dim / vdim lanes: the windowed kind (a window of `window`
     # keys, `rot` rotated lanes, a cap on the scores, a gate on the outputs) and the chunked kind (chunks of `chunk`
     # positions, whole heads rotated; every other one of them borrows the keys and values of the one before);
-    # experts of which a token uses `top`, and a shared one.  The dense feed-forward's width is chosen so that the
-    # model has the parameters of the Qwen2 model beside it.
+    # a dense feed-forward of `ff`; experts of which a token uses `top`, and a shared one
     "1k": dict(width=1024, heads=16, kv_heads=4, dim=64, vdim=64, window=1024, chunk=1024, rot=32, softcap=30.0,
-               experts=8, top=2, expert_ff=704, shared_ff=1408, vocab=32000, layers=8, qwen_inner=2816),
+               ff=2816, experts=8, top=2, expert_ff=704, shared_ff=1408, vocab=32000, layers=8),
     "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, chunk=1024, rot=64, softcap=30.0,
-               experts=8, top=2, expert_ff=1408, shared_ff=2816, vocab=32000, layers=8, qwen_inner=5632),
+               ff=5632, experts=8, top=2, expert_ff=1408, shared_ff=2816, vocab=32000, layers=8),
 }
 
 
-def zobelorn_config(z, ff):
+def zobelorn_config(z):
     """Layers in the pattern chunked + dense, windowed + experts, chunked on the first layer's keys + experts,
     windowed + dense, twice."""
     import tokenizer_b200 as tb
-    dense = {"kind": "dense", "ff": ff}
+    dense = {"kind": "dense", "ff": z["ff"]}
     moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]},
            "shared": {"ff": z["shared_ff"]}}
     heads = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5}
@@ -1355,8 +1354,8 @@ def zobelorn_config(z, ff):
 def run_zobelorn(args):
     """Prefill (one step of 2,048 tokens) and decoding (batch 1 and `--batch`, 2,048-token contexts) of the
     Zobelorn design at two widths, beside the closest model that was there, the Qwen2 decoder (attention in every
-    layer, nothing recurrent), at the same width, depth and heads; the Zobelorn model's dense feed-forward width
-    is chosen so that both have the same parameters.  Then the design's own kernels alone beside the like kernels
+    layer, nothing recurrent), at the same width, depth and heads with the feed-forward width that gives it the
+    same parameters.  Then the design's own kernels alone beside the like kernels
     of the paths that were there, each on inputs larger than L2, against the measured copy peak; the attention
     kernels with and without the cap on the scores, against one another."""
     import torch
@@ -1372,11 +1371,11 @@ def run_zobelorn(args):
     timed = device_timed
     count = lambda config: sum(int(torch.tensor(t.shape).prod()) for t in declared_tensors(config.model_spec()))
 
-    def qwen_config(z):
+    def qwen_config(z, inner):
         return tb.Qwen2Config.from_dict(dict(
             architectures=["Qwen2ForCausalLM"], hidden_act="silu", num_hidden_layers=z["layers"],
             hidden_size=z["width"], num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"],
-            head_dim=z["dim"], intermediate_size=z["qwen_inner"], vocab_size=z["vocab"], rope_theta=1000000.0,
+            head_dim=z["dim"], intermediate_size=inner, vocab_size=z["vocab"], rope_theta=1000000.0,
             rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=32768, use_sliding_window=False,
             sliding_window=32768, max_window_layers=z["layers"]))
 
@@ -1384,11 +1383,13 @@ def run_zobelorn(args):
     for name, z in ZOBELORN_SIZES.items():
         if args.only_kernels:
             break
-        beside = qwen_config(z)
-        base, step = count(zobelorn_config(z, 128)), count(zobelorn_config(z, 256)) - count(zobelorn_config(z, 128))
-        ff = max(1, round((count(beside) - base) / step) + 1) * 128
-        models[name] = {"zobelorn": dict(measure_design(zobelorn_config(z, ff), z["vocab"], args, gen, context, steps), ff=ff),
-                        "qwen2": measure_design(beside, z["vocab"], args, gen, context, steps)}
+        config = zobelorn_config(z)
+        models[name] = {"zobelorn": measure_design(config, z["vocab"], args, gen, context, steps)}
+        # the gated feed-forward width (whole 128s) that brings Qwen2 to the same parameters
+        base, step = count(qwen_config(z, 128)), count(qwen_config(z, 256)) - count(qwen_config(z, 128))
+        inner = max(1, round((count(config) - base) / step) + 1) * 128
+        models[name]["qwen2"] = dict(measure_design(qwen_config(z, inner), z["vocab"], args, gen, context, steps),
+                                     intermediate_size=inner)
 
     # ---- kernels alone: inputs larger than L2, a 256 MB write between the timed launches ----
     dev = "cuda:0"

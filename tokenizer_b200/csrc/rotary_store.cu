@@ -162,11 +162,42 @@ __global__ void attention_gate_kernel(T* __restrict__ out, const TI* __restrict_
   }
 }
 
+// float32 pre-activations, bfloat16 outputs, value heads in whole 8s: eight consecutive lanes a thread
+__global__ void attention_gate_f32_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ proj, int ld,
+                                                 int at, int heads, int vdim, int row, size_t n8) {
+  pdl_wait();
+  pdl_launch();
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const int per_head = vdim / 8, per_row = heads * per_head;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
+    const size_t t = i / per_row;
+    const int c = (int)(i % per_row), head = c / per_head, l = (c % per_head) * 8;
+    const float* g = proj + t * ld + at + head * vdim + l;
+    const float4 g0 = *reinterpret_cast<const float4*>(g), g1 = *reinterpret_cast<const float4*>(g + 4);
+    __nv_bfloat16* o = out + (t * heads + head) * row + l;
+    uint4 raw = *reinterpret_cast<const uint4*>(o);
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+    const float gate[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 v = __bfloat1622float2(h[k]);
+      h[k] = __floats2bfloat162_rn(v.x / (1.0f + expf(-gate[2 * k])), v.y / (1.0f + expf(-gate[2 * k + 1])));
+    }
+    *reinterpret_cast<uint4*>(o) = raw;
+  }
+}
+
 TOKB200_API int tokb200_attention_gate(void* out, int out_dtype, const void* proj, int proj_dtype, int ld, int at,
                                        int n_rows, int heads, int vdim, int row, cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
   if (heads <= 0 || vdim <= 0 || row < vdim || at < 0 || ld < at + heads * vdim) return TOKB200_BAD_SIZE;
   const size_t n = (size_t)n_rows * heads * vdim;
+  if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_BF16 && vdim % 8 == 0 && row % 8 == 0 && ld % 4 == 0 &&
+      at % 4 == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)proj & 15) == 0) {
+    const size_t n8 = n / 8, blocks8 = (n8 + 255) / 256;
+    return launch_dependent(attention_gate_f32_bf16x8_kernel, dim3((unsigned)(blocks8 < 65535 ? blocks8 : 65535)),
+                            dim3(256), 0, stream, (__nv_bfloat16*)out, (const float*)proj, ld, at, heads, vdim, row, n8);
+  }
   const size_t blocks = (n + 255) / 256;
   const dim3 grid((unsigned)(blocks < 8192 ? blocks : 8192));
 #define LAUNCH(TI, T)                                                                                          \
