@@ -18,7 +18,8 @@
 // turned by the angle of frequency i).  `head_norm`: after the rotation every query head and every key
 // head is divided by its own root mean square over its `dim` lanes (`head_eps` inside the root, no gain).
 // A rotation turns pairs and leaves each pair's sum of squares as it was, so a head's mean square is
-// taken of its lanes before the rotation, a warp a head, and kept in shared memory.  `kv_heads` = 0: the
+// taken of its lanes before the rotation, a warp a head, and kept in shared memory.  A token's sines and
+// cosines are computed once a frequency into shared memory (every head turns by the same angles).  `kv_heads` = 0: the
 // projection holds queries only (a layer that reads another layer's cache): nothing is written but q_out.
 //
 // attention_gate: out[t, h, l] *= sigmoid(proj[t, at + h * vdim + l]), l < vdim, on rows of `row` lanes a
@@ -34,17 +35,23 @@ __global__ void qkv_rotate_store_kernel(const TI* __restrict__ proj, int ld, int
                                         int dim, int vdim, int row, const float* __restrict__ q_gain,
                                         const float* __restrict__ k_gain, float eps, const float* __restrict__ temp,
                                         int half_layout, int head_norm, float head_eps) {
-  extern __shared__ float head_inv[];       // heads + kv_heads, with `head_norm`
+  // shared memory: a token's cosines and sines, one pair a frequency (every head turns by the same
+  // angles), then the heads' inverse root mean squares (with `head_norm`)
+  extern __shared__ float shared[];
   __shared__ float scratch[33];
+  const int half = rot_dims >> 1;
+  float* cosine = shared;
+  float* sine = shared + half;
+  float* head_inv = shared + 2 * half;
   const int t = blockIdx.x;
   const int r = row_req[t];
   const int p = pos[t];
   const int where = slot ? slot[t] : -1;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)p * inv_freq[i], &sine[i], &cosine[i]);
   pdl_wait();
   pdl_launch();
   if (r < 0) return;
   const TI* in = proj + (size_t)t * ld + at;
-  const int lanes = (heads + 2 * kv_heads) * row;
   float q_inv = 1.f, k_inv = 1.f;
   if (q_gain != nullptr || k_gain != nullptr) {         // root mean squares over the whole projections
     float qs = 0.f, ks = 0.f;
@@ -57,9 +64,9 @@ __global__ void qkv_rotate_store_kernel(const TI* __restrict__ proj, int ld, int
     if (q_gain != nullptr) q_inv = 1.0f / sqrtf(qs / (float)(heads * dim) + eps);
     if (k_gain != nullptr) k_inv = 1.0f / sqrtf(ks / (float)(kv_heads * dim) + eps);
   }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   if (head_norm) {                                      // a warp a head: the mean square of its lanes
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int head = warp; head < heads + kv_heads; head += blockDim.x >> 5) {
+    for (int head = warp; head < heads + kv_heads; head += warps) {
       const bool query = head < heads;
       const float* gain = query ? q_gain : k_gain;
       const float inv = query ? q_inv : k_inv;
@@ -74,46 +81,49 @@ __global__ void qkv_rotate_store_kernel(const TI* __restrict__ proj, int ld, int
       sum = warp_sum(sum);
       if (lane == 0) head_inv[head] = 1.0f / sqrtf(sum / (float)dim + head_eps);
     }
-    __syncthreads();
   }
-  const int half = rot_dims >> 1;
-  for (int i = threadIdx.x; i < lanes; i += blockDim.x) {
-    const int head = i / row, l = i % row;
-    if (head < heads + kv_heads) {                       // a query or key head: bias, rotation
-      float value = 0.f;
-      if (l < dim) {
-        const int col = head * dim + l;
-        const bool query = head < heads;
-        const float* gain = query ? q_gain : k_gain;
-        const float inv = query ? q_inv : k_inv;
-        const int first = query ? 0 : heads * dim;       // the gains are indexed inside q and inside k
-        value = to_float(in[col]) + (bias ? bias[col] : 0.f);
-        if (gain != nullptr) value = value * inv * gain[col - first];
-        if (l < rot_dims) {
-          const bool second = half_layout ? l >= half : (l & 1);      // the pair's second lane
-          const int mate = half_layout ? (second ? col - half : col + half) : (col ^ 1);
-          float other = to_float(in[mate]) + (bias ? bias[mate] : 0.f);
-          if (gain != nullptr) other = other * inv * gain[mate - first];
-          float s, c;
-          sincosf((float)p * inv_freq[half_layout ? (second ? l - half : l) : (l >> 1)], &s, &c);
-          value = second ? value * c + other * s : value * c - other * s;
+  __syncthreads();                                      // the angles' table (and the heads' norms) are written
+  // a warp a head, a lane every 32nd lane of its row
+  for (int head = warp; head < heads + 2 * kv_heads; head += warps) {
+    if (head < heads + kv_heads) {                       // a query or key head: bias, norms, rotation
+      const bool query = head < heads;
+      T* dst = query ? q_out + ((size_t)t * heads + head) * row
+                     : (where >= 0 ? k_pool + ((size_t)where * kv_heads + (head - heads)) * row : nullptr);
+      if (dst == nullptr) continue;
+      const float* gain = query ? q_gain : k_gain;
+      const float inv = query ? q_inv : k_inv;
+      const int first = query ? 0 : heads * dim;         // the gains are indexed inside q and inside k
+      const float after = (head_norm ? head_inv[head] : 1.f);
+      const float heat = (query && temp != nullptr) ? temp[head] : 1.f;
+      for (int l = lane; l < row; l += 32) {
+        float value = 0.f;
+        if (l < dim) {
+          const int col = head * dim + l;
+          value = to_float(in[col]) + (bias ? bias[col] : 0.f);
+          if (gain != nullptr) value = value * inv * gain[col - first];
+          if (l < rot_dims) {
+            const bool second = half_layout ? l >= half : (l & 1);      // the pair's second lane
+            const int mate = half_layout ? (second ? col - half : col + half) : (col ^ 1);
+            float other = to_float(in[mate]) + (bias ? bias[mate] : 0.f);
+            if (gain != nullptr) other = other * inv * gain[mate - first];
+            const int f = half_layout ? (second ? l - half : l) : (l >> 1);
+            const float c = cosine[f], sn = sine[f];
+            value = second ? value * c + other * sn : value * c - other * sn;
+          }
+          if (head_norm) value *= after;
+          if (query && temp != nullptr) value *= heat;
         }
-        if (head_norm) value *= head_inv[head];
-      }
-      if (head < heads) {
-        if (temp != nullptr) value *= temp[head];
-        q_out[((size_t)t * heads + head) * row + l] = from_float<T>(value);
-      } else if (where >= 0) {
-        k_pool[((size_t)where * kv_heads + (head - heads)) * row + l] = from_float<T>(value);
+        dst[l] = from_float<T>(value);
       }
     } else if (where >= 0) {
       const int g = head - heads - kv_heads;
-      float value = 0.f;
-      if (l < vdim) {
-        const int col = (heads + kv_heads) * dim + g * vdim + l;
-        value = to_float(in[col]) + (bias ? bias[col] : 0.f);
+      T* dst = v_pool + ((size_t)where * kv_heads + g) * row;
+      const int col0 = (heads + kv_heads) * dim + g * vdim;
+      for (int l = lane; l < row; l += 32) {
+        float value = 0.f;
+        if (l < vdim) value = to_float(in[col0 + l]) + (bias ? bias[col0 + l] : 0.f);
+        dst[l] = from_float<T>(value);
       }
-      v_pool[((size_t)where * kv_heads + g) * row + l] = from_float<T>(value);
     }
   }
 }
@@ -127,7 +137,7 @@ TOKB200_API int tokb200_qkv_rotate_store(const void* proj, int proj_dtype, int l
                                          cudaStream_t stream) {
   if (n_rows <= 0) return TOKB200_OK;
   if (kv_heads == 0 && (slot != nullptr || k_gain != nullptr)) return TOKB200_BAD_SIZE;
-  const size_t smem = head_norm ? (size_t)(heads + kv_heads) * sizeof(float) : 0;
+  const size_t smem = (size_t)(rot_dims + (head_norm ? heads + kv_heads : 0)) * sizeof(float);
   if (smem > 40000) return TOKB200_BAD_SIZE;
   if (heads <= 0 || kv_heads < 0 || dim <= 0 || vdim <= 0 || row < dim || row < vdim || rot_dims < 0 ||
       rot_dims % 2 || rot_dims > dim || (rot_dims > 0 && inv_freq == nullptr))
