@@ -98,30 +98,32 @@ def test_norm_parts_of_a_layer_fold_one_plus_and_the_multiplier():
 
 # ---- queries, keys and values: norms, the two layouts of the rotation, queries alone ----------------------
 def rotate_store(proj, pos, heads, kv, dim, vdim, row, dtype, freqs, layout, q_gain=None, k_gain=None, eps=0.0,
-                 head_norm=None, own=True):
+                 head_norm=None, own=True, at=2):
     o = ops()
     n = proj.shape[0]
     q = torch.full((n, heads * row), float("nan"), dtype=dtype, device=DEV)
     pools = [torch.full((n + 3, kv, row), float("nan"), dtype=dtype, device=DEV) for _ in range(2)] if own else [None, None]
     slots = ints(range(n, 0, -1)) if own else None          # rows written back to front, slot 0 left alone
     inv = torch.tensor(freqs, dtype=torch.float64).to(torch.float32).to(DEV) if freqs else None
-    o.qkv_rotate_store(proj, 2, None, inv, 2 * len(freqs), ints(pos), slots, ints([0] * n), q, pools[0], pools[1], heads,
+    o.qkv_rotate_store(proj, at, None, inv, 2 * len(freqs), ints(pos), slots, ints([0] * n), q, pools[0], pools[1], heads,
                        kv if own else 0, dim, vdim, row, q_gain=q_gain, k_gain=k_gain, eps=eps, layout=layout,
                        head_norm_eps=head_norm)
     return q, pools
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,kv,dim,vdim,rot", [(6, 2, 64, 128, 64), (3, 3, 10, 20, 4), (4, 1, 32, 16, 16), (1, 1, 24, 24, 0)])
-def test_whole_projection_norms_then_the_half_layout_on_leading_lanes(heads, kv, dim, vdim, rot, dtype):
+@pytest.mark.parametrize("at", [2, 4])           # behind a column that is a whole 4, sizes in whole 4s take the 16-byte path
+@pytest.mark.parametrize("heads,kv,dim,vdim,rot", [(6, 2, 64, 128, 64), (3, 3, 10, 20, 4), (4, 1, 32, 16, 16), (1, 1, 24, 24, 0),
+                                                   (2, 2, 32, 32, 8)])
+def test_whole_projection_norms_then_the_half_layout_on_leading_lanes(heads, kv, dim, vdim, rot, at, dtype):
     n, eps, factor = 7, 1e-5, 8.0
     row = -(-max(dim, vdim) // 16) * 16
-    proj = rnd(n, 2 + heads * dim + kv * (dim + vdim) + 5, seed=11, scale=2.0)
+    proj = rnd(n, at + heads * dim + kv * (dim + vdim) + 8 - (heads * dim + kv * (dim + vdim)) % 4, seed=11, scale=2.0)
     q_gain, k_gain = rnd(heads * dim, seed=12) + 1.0, rnd(kv * dim, seed=13) + 1.0
     pos = [0, 1, 2, 900, 901, 77, 5000]
     freqs = plain.linear_frequencies(10000.0, rot, factor) if rot else []
-    q, pools = rotate_store(proj, pos, heads, kv, dim, vdim, row, dtype, freqs, "half", q_gain, k_gain, eps)
-    p = proj.double().cpu()[:, 2:]
+    q, pools = rotate_store(proj, pos, heads, kv, dim, vdim, row, dtype, freqs, "half", q_gain, k_gain, eps, at=at)
+    p = proj.double().cpu()[:, at:]
     positions = torch.tensor(pos)
     want_q = plain.root_mean_square_norm(p[:, :heads * dim], eps, q_gain.double().cpu()).view(n, heads, dim)
     want_k = plain.root_mean_square_norm(p[:, heads * dim:(heads + kv) * dim], eps, k_gain.double().cpu()).view(n, kv, dim)
@@ -144,16 +146,18 @@ def test_whole_projection_norms_then_the_half_layout_on_leading_lanes(heads, kv,
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,kv,dim,vdim,rot", [(4, 2, 64, 64, 64), (2, 1, 6, 10, 2), (5, 5, 48, 16, 16), (33, 3, 16, 16, 0)])
-def test_interleaved_rotation_then_a_norm_a_head_without_gain(heads, kv, dim, vdim, rot, dtype):
+@pytest.mark.parametrize("at", [2, 4])
+@pytest.mark.parametrize("heads,kv,dim,vdim,rot", [(4, 2, 64, 64, 64), (2, 1, 6, 10, 2), (5, 5, 48, 16, 16), (33, 3, 16, 16, 0),
+                                                   (3, 1, 24, 40, 8)])
+def test_interleaved_rotation_then_a_norm_a_head_without_gain(heads, kv, dim, vdim, rot, at, dtype):
     n, eps = 6, 1e-6
     row = -(-max(dim, vdim) // 16) * 16
-    proj = rnd(n, 2 + heads * dim + kv * (dim + vdim), seed=15, scale=3.0)
-    proj[:, 2:2 + dim] *= 20.0                            # head 0 far larger than the others: a norm over the whole
+    proj = rnd(n, at + heads * dim + kv * (dim + vdim), seed=15, scale=3.0)
+    proj[:, at:at + dim] *= 20.0                            # head 0 far larger than the others: a norm over the whole
     pos = [0, 3, 64, 65, 1000, 31]                        # projection would leave it so, a norm a head does not
     freqs = plain.banded_frequencies(500.0, rot, 8.0, 1.0, 4.0, 64) if rot else []
-    q, pools = rotate_store(proj, pos, heads, kv, dim, vdim, row, dtype, freqs, "interleaved", head_norm=eps)
-    p, positions = proj.double().cpu()[:, 2:], torch.tensor(pos)
+    q, pools = rotate_store(proj, pos, heads, kv, dim, vdim, row, dtype, freqs, "interleaved", head_norm=eps, at=at)
+    p, positions = proj.double().cpu()[:, at:], torch.tensor(pos)
     want_q = plain.root_mean_square_norm(plain.rotate(p[:, :heads * dim].view(n, heads, dim), positions, freqs, "interleaved"), eps)
     want_k = plain.root_mean_square_norm(
         plain.rotate(p[:, heads * dim:(heads + kv) * dim].view(n, kv, dim), positions, freqs, "interleaved"), eps)
@@ -164,8 +168,8 @@ def test_interleaved_rotation_then_a_norm_a_head_without_gain(heads, kv, dim, vd
     got_sizes = q.view(n, heads, row).float().pow(2).sum(-1).cpu()
     assert float((got_sizes / dim - 1.0).abs().max()) < 0.05          # every head has mean square one
     # queries alone, for a layer that reads another layer's cache: the same queries, nothing else written
-    alone = torch.cat([proj[:, :2 + heads * dim], proj[:, :3]], dim=1).contiguous()
-    q2, _ = rotate_store(alone, pos, heads, kv, dim, vdim, row, dtype, freqs, "interleaved", head_norm=eps, own=False)
+    alone = torch.cat([proj[:, :at + heads * dim], proj[:, :4]], dim=1).contiguous()
+    q2, _ = rotate_store(alone, pos, heads, kv, dim, vdim, row, dtype, freqs, "interleaved", head_norm=eps, own=False, at=at)
     assert torch.equal(q2, q)
 
 

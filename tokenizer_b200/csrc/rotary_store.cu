@@ -26,6 +26,28 @@
 // head: a gate on the heads' outputs that is one more projection of the mixer's input.
 #include "common.cuh"
 
+__device__ __forceinline__ void rs_store4(float* dst, const float v[4]) {
+  *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void rs_store4(__nv_bfloat16* dst, const float v[4]) {
+  __nv_bfloat162 h[2] = {__floats2bfloat162_rn(v[0], v[1]), __floats2bfloat162_rn(v[2], v[3])};
+  *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(h);
+}
+// four consecutive columns of a float32 product from `col` on: + bias, then * inv * gain (each where given)
+__device__ __forceinline__ void rs_load4(const float* in, int col, const float* bias, const float* gain, int gain_col,
+                                         float inv, float v[4]) {
+  const float4 x = *reinterpret_cast<const float4*>(in + col);
+  v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+  if (bias != nullptr) {
+    const float4 b = *reinterpret_cast<const float4*>(bias + col);
+    v[0] += b.x; v[1] += b.y; v[2] += b.z; v[3] += b.w;
+  }
+  if (gain != nullptr) {
+    const float4 g = *reinterpret_cast<const float4*>(gain + gain_col);
+    v[0] = v[0] * inv * g.x; v[1] = v[1] * inv * g.y; v[2] = v[2] * inv * g.z; v[3] = v[3] * inv * g.w;
+  }
+}
+
 template <typename TI, typename T>
 __global__ void qkv_rotate_store_kernel(const TI* __restrict__ proj, int ld, int at, const float* __restrict__ bias,
                                         const float* __restrict__ inv_freq, int rot_dims,
@@ -34,7 +56,7 @@ __global__ void qkv_rotate_store_kernel(const TI* __restrict__ proj, int ld, int
                                         T* __restrict__ k_pool, T* __restrict__ v_pool, int heads, int kv_heads,
                                         int dim, int vdim, int row, const float* __restrict__ q_gain,
                                         const float* __restrict__ k_gain, float eps, const float* __restrict__ temp,
-                                        int half_layout, int head_norm, float head_eps) {
+                                        int half_layout, int head_norm, float head_eps, int quads) {
   // shared memory: a token's cosines and sines, one pair a frequency (every head turns by the same
   // angles), then the heads' inverse root mean squares (with `head_norm`)
   extern __shared__ float shared[];
@@ -83,7 +105,70 @@ __global__ void qkv_rotate_store_kernel(const TI* __restrict__ proj, int ld, int
     }
   }
   __syncthreads();                                      // the angles' table (and the heads' norms) are written
-  // a warp a head, a lane every 32nd lane of its row
+  // a warp a head.  Where every size is whole 4s and everything lies on 16 bytes (`quads`, float32 products):
+  // four consecutive lanes a thread, 16-byte loads, the same arithmetic lane by lane as below.
+  if (sizeof(TI) == 4 && quads) {
+    const float* fin = reinterpret_cast<const float*>(in);
+    for (int head = warp; head < heads + 2 * kv_heads; head += warps) {
+      if (head < heads + kv_heads) {
+        const bool query = head < heads;
+        T* dst = query ? q_out + ((size_t)t * heads + head) * row
+                       : (where >= 0 ? k_pool + ((size_t)where * kv_heads + (head - heads)) * row : nullptr);
+        if (dst == nullptr) continue;
+        const float* gain = query ? q_gain : k_gain;
+        const float inv = query ? q_inv : k_inv;
+        const int first = query ? 0 : heads * dim;
+        const float after = (head_norm ? head_inv[head] : 1.f);
+        const float heat = (query && temp != nullptr) ? temp[head] : 1.f;
+        for (int l = lane * 4; l < row; l += 128) {
+          float v[4] = {0.f, 0.f, 0.f, 0.f};
+          if (l < dim) {
+            const int col = head * dim + l;
+            rs_load4(fin, col, bias, gain, col - first, inv, v);
+            if (l < rot_dims) {
+              if (half_layout) {
+                const bool second = l >= half;
+                const int mate = second ? col - half : col + half;
+                const int f = second ? l - half : l;
+                float m[4];
+                rs_load4(fin, mate, bias, gain, mate - first, inv, m);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  v[j] = second ? v[j] * cosine[f + j] + m[j] * sine[f + j] : v[j] * cosine[f + j] - m[j] * sine[f + j];
+              } else {
+                const int f = l >> 1;
+                const float a0 = v[0], a1 = v[1], a2 = v[2], a3 = v[3];
+                v[0] = a0 * cosine[f] - a1 * sine[f];
+                v[1] = a1 * cosine[f] + a0 * sine[f];
+                v[2] = a2 * cosine[f + 1] - a3 * sine[f + 1];
+                v[3] = a3 * cosine[f + 1] + a2 * sine[f + 1];
+              }
+            }
+            if (head_norm) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) v[j] *= after;
+            }
+            if (query && temp != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) v[j] *= heat;
+            }
+          }
+          rs_store4(dst + l, v);
+        }
+      } else if (where >= 0) {
+        const int g = head - heads - kv_heads;
+        T* dst = v_pool + ((size_t)where * kv_heads + g) * row;
+        const int col0 = (heads + kv_heads) * dim + g * vdim;
+        for (int l = lane * 4; l < row; l += 128) {
+          float v[4] = {0.f, 0.f, 0.f, 0.f};
+          if (l < vdim) rs_load4(fin, col0 + l, bias, nullptr, 0, 1.f, v);
+          rs_store4(dst + l, v);
+        }
+      }
+    }
+    return;
+  }
+  // a lane every 32nd lane of its row
   for (int head = warp; head < heads + 2 * kv_heads; head += warps) {
     if (head < heads + kv_heads) {                       // a query or key head: bias, norms, rotation
       const bool query = head < heads;
@@ -139,6 +224,12 @@ TOKB200_API int tokb200_qkv_rotate_store(const void* proj, int proj_dtype, int l
   if (kv_heads == 0 && (slot != nullptr || k_gain != nullptr)) return TOKB200_BAD_SIZE;
   const size_t smem = (size_t)(rot_dims + (head_norm ? heads + kv_heads : 0)) * sizeof(float);
   if (smem > 40000) return TOKB200_BAD_SIZE;
+  // four lanes a thread: float32 products whose columns, heads and rows are whole 4s (rotated lanes whole 8s, so
+  // that a quad lies inside one half) with every pointer on 16 bytes
+  const uintptr_t all = (uintptr_t)proj | (uintptr_t)bias | (uintptr_t)q_gain | (uintptr_t)k_gain | (uintptr_t)q_out |
+                        (uintptr_t)k_pool | (uintptr_t)v_pool;
+  const int quads = proj_dtype == TOKB200_F32 && dim % 4 == 0 && vdim % 4 == 0 && row % 4 == 0 && rot_dims % 8 == 0 &&
+                    at % 4 == 0 && ld % 4 == 0 && (all & 15) == 0;
   if (heads <= 0 || kv_heads < 0 || dim <= 0 || vdim <= 0 || row < dim || row < vdim || rot_dims < 0 ||
       rot_dims % 2 || rot_dims > dim || (rot_dims > 0 && inv_freq == nullptr))
     return TOKB200_BAD_SIZE;
@@ -146,7 +237,7 @@ TOKB200_API int tokb200_qkv_rotate_store(const void* proj, int proj_dtype, int l
   return launch_dependent(qkv_rotate_store_kernel<TI, T>, dim3(n_rows), dim3(256), smem, stream,              \
                           (const TI*)proj, ld, at, bias, inv_freq, rot_dims, pos, slot, row_req, (T*)q_out,   \
                           (T*)k_pool, (T*)v_pool, heads, kv_heads, dim, vdim, row, q_gain, k_gain, eps, temp, \
-                          half_layout, head_norm, head_eps)
+                          half_layout, head_norm, head_eps, quads)
   if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_F32) LAUNCH(float, float);
   if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_BF16) LAUNCH(float, __nv_bfloat16);
   if (proj_dtype == TOKB200_BF16 && out_dtype == TOKB200_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
