@@ -77,6 +77,14 @@ __global__ void qkv_rotate_store_kernel(const TI* __restrict__ proj, int ld, int
   float q_inv = 1.f, k_inv = 1.f;
   if (q_gain != nullptr || k_gain != nullptr) {         // root mean squares over the whole projections
     float qs = 0.f, ks = 0.f;
+    if (sizeof(TI) == 4 && quads) {
+      for (int col = threadIdx.x * 4; col < (heads + kv_heads) * dim; col += blockDim.x * 4) {
+        float v[4];
+        rs_load4(reinterpret_cast<const float*>(in), col, bias, nullptr, 0, 1.f, v);
+        const float sum = fmaf(v[3], v[3], fmaf(v[2], v[2], fmaf(v[1], v[1], v[0] * v[0])));
+        if (col < heads * dim) qs += sum; else ks += sum;
+      }
+    } else
     for (int col = threadIdx.x; col < (heads + kv_heads) * dim; col += blockDim.x) {
       const float v = to_float(in[col]) + (bias ? bias[col] : 0.f);
       if (col < heads * dim) qs = fmaf(v, v, qs); else ks = fmaf(v, v, ks);
@@ -94,6 +102,13 @@ __global__ void qkv_rotate_store_kernel(const TI* __restrict__ proj, int ld, int
       const float inv = query ? q_inv : k_inv;
       const int first = query ? 0 : heads * dim;
       float sum = 0.f;
+      if (sizeof(TI) == 4 && quads) {
+        for (int l = lane * 4; l < dim; l += 128) {
+          float v[4];
+          rs_load4(reinterpret_cast<const float*>(in), head * dim + l, bias, gain, head * dim + l - first, inv, v);
+          sum += fmaf(v[3], v[3], fmaf(v[2], v[2], fmaf(v[1], v[1], v[0] * v[0])));
+        }
+      } else
       for (int l = lane; l < dim; l += 32) {
         const int col = head * dim + l;
         float v = to_float(in[col]) + (bias ? bias[col] : 0.f);
