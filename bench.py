@@ -1318,9 +1318,9 @@ ZOBELORN_SIZES = {
     # keys, `rot` rotated lanes, a cap on the scores, a gate on the outputs) and the chunked kind (chunks of `chunk`
     # positions, whole heads rotated; every other one of them borrows the keys and values of the one before);
     # a dense feed-forward of `ff`; experts of which a token uses `top`, and a shared one
-    "1k": dict(width=1024, heads=16, kv_heads=4, dim=64, vdim=64, window=1024, chunk=1024, rot=32, softcap=30.0,
+    "1k": dict(width=1024, heads=16, kv_heads=4, dim=64, vdim=64, window=1024, chunk=1024, rot=32, softcap=50.0,
                ff=2816, experts=8, top=2, expert_ff=704, shared_ff=1408, vocab=32000, layers=8),
-    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, chunk=1024, rot=64, softcap=30.0,
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, chunk=1024, rot=64, softcap=50.0,
                ff=5632, experts=8, top=2, expert_ff=1408, shared_ff=2816, vocab=32000, layers=8),
 }
 
@@ -1334,9 +1334,9 @@ def zobelorn_config(z):
            "shared": {"ff": z["shared_ff"]}}
     heads = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5}
     windowed = dict(heads, mask={"size": z["window"]}, softcap=z["softcap"],
-                    rot={"base": 1000000.0, "dims": z["rot"], "scaling": {"factor": 8.0}})
+                    rot={"base": 10000.0, "dims": z["rot"], "scaling": {"factor": 4.0}})
     chunked = dict(heads, mask={"size": z["chunk"]},
-                   rot={"base": 20000.0, "dims": z["dim"], "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 512}})
+                   rot={"base": 500000.0, "dims": z["dim"], "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})
     layers = []
     for i in range(z["layers"]):
         kind = i % 4
@@ -1348,7 +1348,7 @@ def zobelorn_config(z):
             layers.append({"type": "attention", "mixer": windowed, "mlp": moe if kind == 1 else dense})
     return tb.config.ZobelornConfig.from_dict({
         "architecture": "Zobelorn", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
-        "embedding": {"scale": 16.0}, "residual_mult": 0.3, "layers": layers})
+        "embedding": {"scale": 32.0}, "residual_mult": 0.5, "layers": layers})
 
 
 def run_zobelorn(args):
@@ -1440,7 +1440,7 @@ def run_zobelorn(args):
     v_pool = torch.zeros_like(k_pool)
     qg, kg = torch.ones(nh * d, device=dev), torch.ones(nkv * d, device=dev)
     freq64 = torch.tensor([1e6 ** (-2.0 * i / 64) for i in range(32)], device=dev)
-    freq128 = torch.tensor([2e4 ** (-2.0 * i / 128) for i in range(64)], device=dev)
+    freq128 = torch.tensor([5e5 ** (-2.0 * i / 128) for i in range(64)], device=dev)
     qkv_bytes = T * (nh + 2 * nkv) * d * (4 + 2)
     record(f"qkv_rotate_store, whole-projection norms and 64 lanes rotated by halves, {T} tokens, {nh} heads over {nkv} of {d}",
            kernel_time(lambda: ops.qkv_rotate_store(wide, 0, None, freq64, 64, pos, pos, req, q_out, k_pool, v_pool, nh, nkv, d, d, d,
@@ -1499,7 +1499,7 @@ def run_zobelorn(args):
         window = 1023
         # a row of the portion reads the 1,024 keys of its window: two products of 2 * d a key and head
         flops = n_req * portion * nh * 1024 * 4 * d
-        for cap in (None, 30.0):
+        for cap in (None, 50.0):
             record(f"{kernel}, {n_req} portions of {portion} rows, a window of 1,024 keys, " + ("capped" if cap else "no cap"),
                    kernel_time(lambda: run(q, k_pool, v_pool, out, table, row_req, pos, tiles, n_tiles, nh, nkv, d, page, window,
                                            d ** -0.5, softcap=cap)), 0, None if cap is None else kernel + ", no cap", flops=flops)
@@ -1511,7 +1511,7 @@ def run_zobelorn(args):
     out1 = torch.empty_like(q1)
     req1 = torch.arange(rows, dtype=torch.int32, device=dev)
     pos1 = torch.full((rows,), n_keys - 1, dtype=torch.int32, device=dev)
-    for cap in (None, 30.0):
+    for cap in (None, 50.0):
         record(f"decode_attention, {rows} rows x {n_keys} keys, " + ("capped" if cap else "no cap"),
                kernel_time(lambda: ops.decode_attention(q1, big_k, big_v, out1, table, req1, pos1, nh, nkv, d, page, None,
                                                         d ** -0.5, softcap=cap)), rows * n_keys * nkv * d * 4,

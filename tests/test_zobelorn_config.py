@@ -119,7 +119,7 @@ def test_the_model_spec_names_parts_that_other_designs_can_use():
         ["sandwich_norm_residual"] * 2
     assert all(l.parts["mixer"].kind == "gqa_rotary" for l in spec.layers)
     assert all(l.parts["mixer_norm"].kind == "rms_norm" and l.parts["mixer_norm"].params["one_plus"] for l in spec.layers)
-    assert spec.layers[0].parts["mixer_post_norm"].params["gain_scale"] == 0.3
+    assert spec.layers[0].parts["mixer_post_norm"].params["gain_scale"] == 0.35
     assert "gain_scale" not in spec.layers[0].parts["mixer_norm"].params and "gain_scale" not in spec.final_norm.params
     routed = spec.layers[1].parts["feed_forward"].params
     assert (routed["score"], routed["share_on"], routed["shared_gate"], routed["top"]) == ("sigmoid", "input", False, 3)

@@ -155,7 +155,7 @@ def test_interleaved_rotation_then_a_norm_a_head_without_gain(heads, kv, dim, vd
     proj = rnd(n, at + heads * dim + kv * (dim + vdim), seed=15, scale=3.0)
     proj[:, at:at + dim] *= 20.0                            # head 0 far larger than the others: a norm over the whole
     pos = [0, 3, 64, 65, 1000, 31]                        # projection would leave it so, a norm a head does not
-    freqs = plain.banded_frequencies(500.0, rot, 8.0, 1.0, 4.0, 64) if rot else []
+    freqs = plain.banded_frequencies(500.0, rot, 8.0, 1.0, 3.0, 64) if rot else []
     q, pools = rotate_store(proj, pos, heads, kv, dim, vdim, row, dtype, freqs, "interleaved", head_norm=eps, at=at)
     p, positions = proj.double().cpu()[:, at:], torch.tensor(pos)
     want_q = plain.root_mean_square_norm(plain.rotate(p[:, :heads * dim].view(n, heads, dim), positions, freqs, "interleaved"), eps)
@@ -511,7 +511,7 @@ def test_sizes_that_tiny_models_make_equal_or_one(tmp_path_factory):
     ones = config([windowed(1, 1, 16, 16, 0.25, size=2, rot=(10.0, 2, 1.0), softcap=1.0, mlp=moe(1, 1, 8)),
                    chunked(1, 1, 8, 8, 0.35, size=2, rot=(10.0, 2, (2.0, 1.0, 2.0, 8)), mlp=moe(2, 1, 8, shared=8))],
                   vocab=40, width=16, eps=1e-6, scale=1.0, mult=1.0)
-    bands = (8.0, 1.0, 4.0, 128)
+    bands = (8.0, 1.0, 5.0, 128)
     borrowers = config([chunked(4, 2, 32, 32, 0.18, size=48, rot=(1000.0, 32, bands), mlp=dense(48))] +
                        [chunked(4, 2, 32, 32, 0.18, size=48 // (i + 1), rot=(1000.0, 32, bands), kv_from=0, mlp=dense(24))
                         for i in range(3)], vocab=90, width=48, eps=1e-6, scale=2.0, mult=0.6)

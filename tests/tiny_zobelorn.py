@@ -68,9 +68,9 @@ def tiny_b():
     """Sizes the tensor-core kernels take (cache rows of 64 and 128 lanes): chunks of 100 that do not fit the
     pages, a window of 130 with whole heads rotated and no scaling, a layer that borrows keys two layers back,
     one expert a token and no shared one, no multiplier on the residual."""
-    return config([chunked(4, 2, 64, 64, 0.125, size=100, rot=(20000.0, 64, (8.0, 1.0, 4.0, 256)), mlp=moe(4, 1, 64)),
-                   windowed(2, 2, 128, 96, 0.09, size=130, rot=(1000000.0, 128, None), softcap=20.0, mlp=dense(256)),
-                   chunked(4, 2, 64, 64, 0.11, size=100, rot=(20000.0, 64, (8.0, 1.0, 4.0, 256)), kv_from=0, mlp=dense(128))],
+    return config([chunked(4, 2, 64, 64, 0.125, size=100, rot=(5000.0, 64, (6.0, 1.0, 3.0, 256)), mlp=moe(4, 1, 64)),
+                   windowed(2, 2, 128, 96, 0.09, size=130, rot=(800000.0, 128, None), softcap=20.0, mlp=dense(256)),
+                   chunked(4, 2, 64, 64, 0.11, size=100, rot=(5000.0, 64, (6.0, 1.0, 3.0, 256)), kv_from=0, mlp=dense(128))],
                   vocab=1000, width=128, eps=1e-6, scale=1.0, mult=1.0), 4, 16
 
 
@@ -94,7 +94,7 @@ def tiny_d():
                    windowed(6, 3, 16, 32, 0.25, size=50, rot=(50.0, 16, 1.5), softcap=50.0),
                    chunked(2, 1, 48, 16, 0.2, rot=(300.0, 16, bands), kv_from=0, mlp=dense(40)),
                    windowed(2, 2, 32, 32, 0.18, size=4096, rot=(10000.0, 32, 8.0), mlp=dense(64))],
-                  vocab=120, width=64, eps=2e-6, scale=4.0, mult=0.3), 6, 16
+                  vocab=120, width=64, eps=2e-6, scale=4.0, mult=0.35), 6, 16
 
 
 TINY = {"a": tiny_a, "b": tiny_b, "c": tiny_c, "d": tiny_d}
