@@ -367,11 +367,37 @@ LENGTHS = {"a": [1, 2, 23, 100, 131, 49], "b": [5, 19, 97, 201, 260, 100], "c": 
            "d": [4, 31, 77, 150, 9, 60]}
 
 
+def close_calls(raw, w, ids, below=0.03):
+    """The positions of `ids` at which some layer of experts chooses between two scores closer than `below`, from the
+    plain implementation: there the rounding of bfloat16 anywhere upstream decides which expert is used (the router is
+    left as drawn), so the comparisons in bfloat16 leave these positions out; in float32 nothing is left out."""
+    found, inner = set(), plain.routed_feed_forward
+
+    def spy(h, weights, prefix, mlp):
+        scores = plain.sigmoid(plain.linear(h, weights[prefix + ".router"])).sort(dim=1, descending=True).values
+        top = mlp["router"]["top"]
+        if scores.shape[1] > top:
+            found.update(int(t) for t in ((scores[:, top - 1] - scores[:, top]) < below).nonzero()[:, 0])
+        return inner(h, weights, prefix, mlp)
+    plain.routed_feed_forward = spy
+    try:
+        plain.forward(raw, w, list(ids))
+    finally:
+        plain.routed_feed_forward = inner
+    return found
+
+
+_CLOSE_CALLS = {}     # id of a fixture's reference logits -> {request: positions with a close call}
+
+
 @pytest.fixture(scope="module", params=sorted(TINY))
 def model(request, tmp_path_factory):
     folder, cfg, page = make_folder(tmp_path_factory, request.param)
     requests = {f"r{i}": random_ids(n, cfg.vocab, 300 + i) for i, n in enumerate(LENGTHS[request.param])}
-    return folder, cfg, page, requests, reference_logits(folder, requests)
+    want = reference_logits(folder, requests)
+    raw, w = plain.load_folder(folder)
+    _CLOSE_CALLS[id(want)] = {name: close_calls(raw, w, ids) for name, ids in requests.items()}
+    return folder, cfg, page, requests, want
 
 
 def replay(folder, dtype, steps, max_tokens, page, max_requests=4, use_graphs=True):
@@ -402,14 +428,17 @@ def compare(got, want, dtype, what):
     """float32: every logit within 1e-4.  bfloat16: per position, the root mean square of the difference (its
     mean over the vocabulary taken off) against that of the logits themselves: the operands' rounding (2^-9
     each) reaches the logits of these tiny models at about one part in a hundred, while a key, a window's edge
-    or an expert's weight that is wrong moves a position's logits by their own size.  A token whose two best
-    experts score within rounding of one another may choose the other in bfloat16 (the router is left as
-    drawn), which moves that position alone: two positions in a hundred may lie beyond the bound."""
+    or an expert's weight that is wrong moves a position's logits by their own size.  Positions at which the
+    choice of experts is a close call (`close_calls`) are left out; a token that chose another expert still sits
+    in the cache of the tokens behind it, so two positions in a hundred may lie beyond the bound."""
     if dtype == "float32":
         return ru.compare(got, want, dtype, what)
     rel, where = [], []
+    skip = _CLOSE_CALLS.get(id(want), {})
     for name in sorted(got):
         for position in sorted(got[name]):
+            if position in skip.get(name, ()):
+                continue
             row, ref = got[name][position], want[name][position]
             assert np.isfinite(row).all(), f"{what}: {name}[{position}] not finite"
             d, c = row - ref, ref - ref.mean()
@@ -549,6 +578,10 @@ def near_best(cfg, w, prompt, tokens, dtype):
     chosen = lead.gather(1, torch.tensor(tokens)[:, None])[:, 0]
     slack = 1e-4 if dtype == "float32" else 0.1 * float(logits.abs().max())
     gap = lead.max(dim=1).values - chosen
+    if dtype != "float32":      # a token chosen where the experts' choice is a close call says nothing in bfloat16
+        for position in close_calls(cfg, w, list(prompt) + list(tokens)):
+            if len(prompt) - 1 <= position < len(prompt) - 1 + len(tokens):
+                gap[position - (len(prompt) - 1)] = 0.0
     assert float(gap.max()) <= slack, f"token {int(gap.argmax())} lies {float(gap.max())} below the best logit"
 
 
