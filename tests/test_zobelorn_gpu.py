@@ -98,13 +98,13 @@ def test_norm_parts_of_a_layer_fold_one_plus_and_the_multiplier():
 
 # ---- queries, keys and values: norms, the two layouts of the rotation, queries alone ----------------------
 def rotate_store(proj, pos, heads, kv, dim, vdim, row, dtype, freqs, layout, q_gain=None, k_gain=None, eps=0.0,
-                 head_norm=None, own=True, at=2):
+                 head_norm=None, own=True, at=2, wide=False):
     o = ops()
     n = proj.shape[0]
     q = torch.full((n, heads * row), float("nan"), dtype=dtype, device=DEV)
     pools = [torch.full((n + 3, kv, row), float("nan"), dtype=dtype, device=DEV) for _ in range(2)] if own else [None, None]
     slots = ints(range(n, 0, -1)) if own else None          # rows written back to front, slot 0 left alone
-    inv = torch.tensor(freqs, dtype=torch.float64).to(torch.float32).to(DEV) if freqs else None
+    inv = torch.tensor(freqs, dtype=torch.float64).to(torch.float64 if wide else torch.float32).to(DEV) if freqs else None
     o.qkv_rotate_store(proj, at, None, inv, 2 * len(freqs), ints(pos), slots, ints([0] * n), q, pools[0], pools[1], heads,
                        kv if own else 0, dim, vdim, row, q_gain=q_gain, k_gain=k_gain, eps=eps, layout=layout,
                        head_norm_eps=head_norm)
@@ -171,6 +171,23 @@ def test_interleaved_rotation_then_a_norm_a_head_without_gain(heads, kv, dim, vd
     alone = torch.cat([proj[:, :at + heads * dim], proj[:, :4]], dim=1).contiguous()
     q2, _ = rotate_store(alone, pos, heads, kv, dim, vdim, row, dtype, freqs, "interleaved", head_norm=eps, own=False, at=at)
     assert torch.equal(q2, q)
+
+
+@pytest.mark.parametrize("layout", ["half", "interleaved"])
+def test_angles_taken_in_64_bit_stay_exact_far_out(layout):
+    """Frequencies handed over in 64-bit: the angle position * frequency is formed in 64-bit and brought into one
+    turn before it is rounded, so a rotation at position 900,000 is as exact as one at position 9 (the 32-bit
+    product is good to 6e-8 of the angle, 0.05 radians out there)."""
+    n, heads, kv, dim, row = 5, 2, 1, 32, 32
+    proj = rnd(n, heads * dim + kv * 2 * dim, seed=17)
+    pos = [9, 5000, 70001, 900000, 899999]
+    freqs = plain.linear_frequencies(10000.0, 16, 1.0)
+    p, positions = proj.double().cpu(), torch.tensor(pos)
+    want = plain.rotate(p[:, :heads * dim].view(n, heads, dim), positions, freqs, layout)
+    q, _ = rotate_store(proj, pos, heads, kv, dim, dim, row, torch.float32, freqs, layout, at=0, wide=True)
+    close(q.view(n, heads, row), want, torch.float32, "64-bit angles", 2e-6)
+    q32, _ = rotate_store(proj, pos, heads, kv, dim, dim, row, torch.float32, freqs, layout, at=0)
+    assert float((q32.view(n, heads, row).double().cpu() - want).abs().max()) > 1e-3
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -1,7 +1,8 @@
 // Queries, keys and values of an attention layer whose key and value heads differ in size, from one
 // stacked product: the projection's bias, the rotation of the leading `rot_dims` lanes of every query
 // and key head in the interleaved form (lane 2i pairs with lane 2i + 1; the pair (u, v) at position p
-// becomes (u cos a - v sin a, v cos a + u sin a), a = float32(p) * inv_freq[i]), and the write of the
+// becomes (u cos a - v sin a, v cos a + u sin a), a = float32(p) * inv_freq[i], or, where the frequencies come
+// in 64-bit (`inv_freq64`), the 64-bit product brought into one turn before it is rounded), and the write of the
 // token's keys and values into its cache slot.  Cache rows and query rows have `row` lanes a head,
 // row >= max(dim, vdim): keys and queries fill the first `dim` lanes, values the first `vdim`, the
 // rest is written as zero, so that kernels which take one head size serve both.
@@ -50,7 +51,8 @@ __device__ __forceinline__ void rs_load4(const float* in, int col, const float* 
 
 template <typename TI, typename T>
 __global__ void qkv_rotate_store_kernel(const TI* __restrict__ proj, int ld, int at, const float* __restrict__ bias,
-                                        const float* __restrict__ inv_freq, int rot_dims,
+                                        const float* __restrict__ inv_freq,
+                                        const double* __restrict__ inv_freq64, int rot_dims,
                                         const int* __restrict__ pos, const int* __restrict__ slot,
                                         const int* __restrict__ row_req, T* __restrict__ q_out,
                                         T* __restrict__ k_pool, T* __restrict__ v_pool, int heads, int kv_heads,
@@ -69,7 +71,17 @@ __global__ void qkv_rotate_store_kernel(const TI* __restrict__ proj, int ld, int
   const int r = row_req[t];
   const int p = pos[t];
   const int where = slot ? slot[t] : -1;
-  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)p * inv_freq[i], &sine[i], &cosine[i]);
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float angle;
+    if (inv_freq64 != nullptr) {       // the product and its reduction to one turn in 64-bit: good to 1e-7 at any position
+      double a = (double)p * inv_freq64[i];
+      a -= 6.283185307179586476925 * rint(a * 0.15915494309189533577);
+      angle = (float)a;
+    } else {
+      angle = (float)p * inv_freq[i];
+    }
+    sincosf(angle, &sine[i], &cosine[i]);
+  }
   pdl_wait();
   pdl_launch();
   if (r < 0) return;
@@ -229,7 +241,8 @@ __global__ void qkv_rotate_store_kernel(const TI* __restrict__ proj, int ld, int
 }
 
 TOKB200_API int tokb200_qkv_rotate_store(const void* proj, int proj_dtype, int ld, int at, const float* bias,
-                                         const float* inv_freq, int rot_dims, const int* pos, const int* slot,
+                                         const float* inv_freq, const double* inv_freq64, int rot_dims,
+                                         const int* pos, const int* slot,
                                          const int* row_req, void* q_out, void* k_pool, void* v_pool,
                                          int out_dtype, int n_rows, int heads, int kv_heads, int dim, int vdim,
                                          int row, const float* q_gain, const float* k_gain, float eps,
@@ -246,11 +259,12 @@ TOKB200_API int tokb200_qkv_rotate_store(const void* proj, int proj_dtype, int l
   const int quads = proj_dtype == TOKB200_F32 && dim % 4 == 0 && vdim % 4 == 0 && row % 4 == 0 && rot_dims % 8 == 0 &&
                     at % 4 == 0 && ld % 4 == 0 && (all & 15) == 0;
   if (heads <= 0 || kv_heads < 0 || dim <= 0 || vdim <= 0 || row < dim || row < vdim || rot_dims < 0 ||
-      rot_dims % 2 || rot_dims > dim || (rot_dims > 0 && inv_freq == nullptr))
+      rot_dims % 2 || rot_dims > dim || (rot_dims > 0 && inv_freq == nullptr && inv_freq64 == nullptr))
     return TOKB200_BAD_SIZE;
 #define LAUNCH(TI, T)                                                                                         \
   return launch_dependent(qkv_rotate_store_kernel<TI, T>, dim3(n_rows), dim3(256), smem, stream,              \
-                          (const TI*)proj, ld, at, bias, inv_freq, rot_dims, pos, slot, row_req, (T*)q_out,   \
+                          (const TI*)proj, ld, at, bias, inv_freq, inv_freq64, rot_dims, pos, slot, row_req,  \
+                          (T*)q_out,                                                                          \
                           (T*)k_pool, (T*)v_pool, heads, kv_heads, dim, vdim, row, q_gain, k_gain, eps, temp, \
                           half_layout, head_norm, head_eps, quads)
   if (proj_dtype == TOKB200_F32 && out_dtype == TOKB200_F32) LAUNCH(float, float);

@@ -1262,7 +1262,8 @@ def qkv_rotate_store(proj: torch.Tensor, at: int, bias, inv_freq, rot_dims: int,
     inside the root) and multiplied by the gain first; `temp` (float32, one a query head) multiplies
     the head's queries.  `layout` "half": lane i of the rotated lanes pairs with lane i + rot_dims / 2 instead.
     `head_norm_eps` (a number): after the rotation every query and key head is divided by its own root mean
-    square over its dim lanes, that eps inside the root.  `kv_heads` 0: `proj` holds queries only and nothing
+    square over its dim lanes, that eps inside the root.  `inv_freq` float64: the angle position * frequency is
+    taken in 64-bit and brought into one turn before its sine and cosine (float32: the 32-bit product).  `kv_heads` 0: `proj` holds queries only and nothing
     but `q_out` is written (`slot`, `k_pool`, `v_pool` None)."""
     n = proj.shape[0]
     if layout not in ("interleaved", "half"):
@@ -1276,8 +1277,10 @@ def qkv_rotate_store(proj: torch.Tensor, at: int, bias, inv_freq, rot_dims: int,
     for gain, size in ((q_gain, heads * dim), (k_gain, kv_heads * dim), (temp, heads)):
         if gain is not None and (gain.dtype != torch.float32 or gain.numel() != size):
             raise ValueError("qkv_rotate_store: gains are float32, one a column of q and of k; temperatures one a head")
+    wide = inv_freq is not None and inv_freq.dtype == torch.float64      # frequencies in 64-bit: the angle is too
     _check(_lib("rotary_store").tokb200_qkv_rotate_store(
-        _sliced_ptr(proj), _i(_tag(proj)), _i(_ld(proj)), _i(at), _ptr(bias), _ptr(inv_freq), _i(rot_dims), _ptr(pos),
+        _sliced_ptr(proj), _i(_tag(proj)), _i(_ld(proj)), _i(at), _ptr(bias), _ptr(None if wide else inv_freq),
+        _ptr(inv_freq if wide else None), _i(rot_dims), _ptr(pos),
         _ptr(slot), _ptr(row_req), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _i(_tag(q_out)), _i(n), _i(heads),
         _i(kv_heads), _i(dim), _i(vdim), _i(row), _ptr(q_gain), _ptr(k_gain), _f(eps), _ptr(temp),
         _i(int(layout == "half")), _i(int(head_norm_eps is not None)), _f(head_norm_eps or 0.0), _stream()),

@@ -483,7 +483,7 @@ class RotaryGQAttention(PagedAttention):
             raise ValueError("a layer with keys of its own writes its cache; one without reads an earlier call's")
         group = ctx.groups[cache.group]
         q = self.runtime.empty(ctx.n_tokens, self.nh * self.row)
-        ops.qkv_rotate_store(proj, at, self.bias, self.position.inv_freq if self.position is not None else None,
+        ops.qkv_rotate_store(proj, at, self.bias, self.position.inv_freq64 if self.position is not None else None,
                              self.rot_dims, ctx.pos, group.slots if cache.writes else None, ctx.row_req, q,
                              cache.k_pool if self.own_kv else None, cache.v_pool if self.own_kv else None, self.nh,
                              self.nkv if self.own_kv else 0, self.dim, self.vdim, self.row,

@@ -87,6 +87,9 @@ class RotaryInterleaved:
         freq = scaled_frequencies([self.base ** (-2.0 * i / self.dims) for i in range(self.dims // 2)],
                                   spec.params.get("scaling"))
         self.inv_freq = torch.tensor(freq, dtype=torch.float64).to(torch.float32).to(runtime.device)
+        # the same in 64-bit, for kernels that take the angle in 64-bit (an angle of thousands of radians
+        # carries the 32-bit product's rounding, 6e-8 of itself, straight into its sine)
+        self.inv_freq64 = torch.tensor(freq, dtype=torch.float64).to(runtime.device)
 
 
 class RotaryHalfComputed(RotaryInterleaved):
