@@ -1439,8 +1439,9 @@ def run_zobelorn(args):
     k_pool = torch.zeros(T + 64, nkv, d, dtype=torch.bfloat16, device=dev)
     v_pool = torch.zeros_like(k_pool)
     qg, kg = torch.ones(nh * d, device=dev), torch.ones(nkv * d, device=dev)
-    freq64 = torch.tensor([1e6 ** (-2.0 * i / 64) for i in range(32)], device=dev)
-    freq128 = torch.tensor([5e5 ** (-2.0 * i / 128) for i in range(64)], device=dev)
+    # frequencies in 64-bit, as the position part hands them over (the angle is then formed in 64-bit)
+    freq64 = torch.tensor([1e6 ** (-2.0 * i / 64) for i in range(32)], dtype=torch.float64, device=dev)
+    freq128 = torch.tensor([5e5 ** (-2.0 * i / 128) for i in range(64)], dtype=torch.float64, device=dev)
     qkv_bytes = T * (nh + 2 * nkv) * d * (4 + 2)
     record(f"qkv_rotate_store, whole-projection norms and 64 lanes rotated by halves, {T} tokens, {nh} heads over {nkv} of {d}",
            kernel_time(lambda: ops.qkv_rotate_store(wide, 0, None, freq64, 64, pos, pos, req, q_out, k_pool, v_pool, nh, nkv, d, d, d,
